@@ -5,6 +5,7 @@ from .spec import BranchSpec, LayerSpec, ModelSpec, PartSpec, ScheduleEntry, pre
 from .llama import LlamaConfig, build_llama_spec, llama_config_from_dict
 from .rigozen import RigozenConfig, build_rigozen_spec, rigozen_config_from_dict
 from .losorax import LosoraxConfig, build_losorax_spec, losorax_config_from_dict
+from .virorax import ViroraxConfig, build_virorax_spec, virorax_config_from_dict
 from .presets import PRESETS, preset
 
 __all__ = [
@@ -14,4 +15,5 @@ __all__ = [
     "LlamaConfig", "build_llama_spec", "llama_config_from_dict", "PRESETS", "preset",
     "RigozenConfig", "build_rigozen_spec", "rigozen_config_from_dict",
     "LosoraxConfig", "build_losorax_spec", "losorax_config_from_dict",
+    "ViroraxConfig", "build_virorax_spec", "virorax_config_from_dict",
 ]

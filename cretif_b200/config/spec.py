@@ -30,12 +30,13 @@ class PartSpec:
 
 @dataclass(frozen=True)
 class BranchSpec:
-    """One residual branch of a block: ``h += post_norm(part(shift(norm(h))))``.
+    """One residual branch of a block: ``h += scale * post_norm(part(shift(norm(h))))``.
 
     ``role`` is the part's category (``"mixer"`` or ``"feed_forward"``); ``norm`` stands
     before the part and ``post_norm`` after it, and either may be absent.  ``shift`` (a part
     of the ``shift`` category, optional) stands between the norm and the part: it blends each
     token's row with the row of the token before it and keeps a row per sequence between steps.
+    ``scale`` multiplies what the branch adds to the stream (a residual multiplier; 1 for none).
     """
 
     role: str
@@ -43,6 +44,7 @@ class BranchSpec:
     norm: Optional[PartSpec] = None
     post_norm: Optional[PartSpec] = None
     shift: Optional[PartSpec] = None
+    scale: float = 1.0
 
 
 @dataclass(frozen=True)
@@ -82,10 +84,14 @@ class ScheduleEntry:
     the keys and values that schedule entry ``j`` (an earlier one) writes, without
     writing.  What a visit's parts keep per sequence in fixed size (a recurrent state,
     the last inputs of a convolution, a shifted row) is always the visit's own.
+    ``add_input`` adds the model's input (the embedding part's output, as it was before the
+    first layer) to the residual stream once more, right before this visit: a model that runs
+    a span of layers several times over feeds each further pass that way.
     """
 
     layer: int
     cache: Optional[int] = None
+    add_input: bool = False
 
 
 @dataclass

@@ -10,10 +10,12 @@
 extern "C" {
 #endif
 
-// out[t, :] = table[ids[t], :] widened to float32.  An id outside [0, V) sets bit 1 of
-// *fault and writes zeros.
+// out[t, :] = table[ids[t], :] widened to float32 (+ pos_table[tok_pos[t], :] when a table of P
+// learned position vectors is given).  An id outside [0, V), or a position outside [0, P), sets
+// bit 1 of *fault and writes zeros.
 int cretif_embed_rows(const void* table, int table_dt, const int* ids, float* out, int T, int H,
-                      int V, unsigned int* fault, void* stream);
+                      int V, unsigned int* fault, const void* pos_table, const int* tok_pos, int P,
+                      void* stream);
 
 // v = h[src] (+ delta[src]); if write_h, h[src] = v; out[r] = v * weight * rsqrt(mean(v^2)+eps).
 // src = rows ? rows[r] : r.  delta may be null.  rows and write_h exclude each other.
@@ -316,6 +318,47 @@ int cretif_attn_prefill_tc_bias(const void* qkv, int ldq, int T, void* out, int 
                                 float scale, int window, int bt, int B, int max_new,
                                 const float* sink, const float* bias_near, const float* bias_far,
                                 int n_far, unsigned int* fault, void* stream);
+
+// Per-head work of an attention whose projections are normed head by head (head_ops.cu).
+// proj rows [q (nh hd) | k (nkv hd) | v (nkv vd) | ...] (float32 or bfloat16): + bias (null for
+// none), RMS norm of every q and k head times wq / wk (hd numbers each, both null for none),
+// rotation of the first rot_dim channels by the position (pairing 0: (i, i + rot_dim/2), 1:
+// (2i, 2i+1)); q to q_out, k and v into the block cache (write_cache; else only q is made).
+int cretif_headnorm_rope_kv_append(const void* proj, int ldp, int proj_dt, const float* bias,
+                                   const float* wq, const float* wk, float eps, const float* cos_t,
+                                   const float* sin_t, int pairing, int rot_dim,
+                                   const int* tok_pos, const int* tok_seq, const int* seq_slot,
+                                   int nh, int nkv, int hd, int vd, void* q_out, int ldq, int dt,
+                                   const int* table, int table_stride, void* kc, void* vc, int bt,
+                                   int write_cache, int T, unsigned int* fault, void* stream);
+// o[t, h, :] *= sigmoid(g[t, h]) for nh heads of vd channels.
+int cretif_gate_heads(void* o, int ldo, int dt, const float* g, int ldg, int nh, int vd, int T,
+                      void* stream);
+// out = act(in) element by element: kind 0 relu(z)^2, 1 gelu in its tanh form, 2 silu.
+int cretif_activation(const void* in, int ldi, int in_dt, void* out, int ldo, int out_dt, int T,
+                      int width, int kind, void* stream);
+// z <- cap * tanh(z / cap) in place.
+int cretif_softcap(float* z, long long total, float cap, void* stream);
+// h += alpha * y over `total` elements (y float32 or bfloat16).
+int cretif_axpy_rows(float* h, const void* y, int y_dt, float alpha, long long total,
+                     void* stream);
+
+// Retention (retention.cu).  proj rows (float32): [q (H d) | k (H d) | ...]; prep rows: the
+// rotated q and the rotated k times k_scale.  state points at the first sequence slot's
+// matrices [H, d, e]; state_stride is a slot's size in floats.  o_raw [T, H e] receives the
+// read-outs S^T q after S <- decay_h S + k v^T.
+int cretif_retention_prepare(const float* proj, int ldp, float* prep, int ldo, const float* cos_t,
+                             const float* sin_t, int pairing, int rot_dim, const int* tok_pos,
+                             int H, int d, float k_scale, int T, void* stream);
+int cretif_retention_recurrence(const float* prep, int ldp, const float* v, int ldv,
+                                const float* decay, float* state, long long state_stride,
+                                const int* cu_seqlens, const int* seq_slot, int B, int H, int d,
+                                int e, float* o_raw, int write_state, int T, void* stream);
+// out = o_raw / rms(o_raw) per head [* norm_w] * gate(gate): norm_w null, of e numbers, or of
+// H e (per_head_weight); the gate is SiLU or the logistic function (gate_sigmoid).
+int cretif_heads_out_norm(const float* o_raw, const float* gate, int ldg, const float* norm_w,
+                          int per_head_weight, int gate_sigmoid, float eps, void* out, int out_dt,
+                          int ldo, int H, int e, int T, void* stream);
 
 // One CTA waits, with the library's bounded wait, on a barrier that nothing completes; after
 // `limit` polls (at most 2^20) it gives up, sets bit 2 of *fault and returns.  *polls (may be

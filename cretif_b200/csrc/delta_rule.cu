@@ -299,12 +299,13 @@ delta_out_norm_kernel(const float* __restrict__ o_raw, const float* __restrict__
   const float inv = 1.0f / sqrtf(ss / (float)e + eps);
   // w_stride: 0 when the heads share one weight of e numbers, e when each has its own;
   // the gate is SiLU or, with gate_sigmoid, the logistic function alone
-  const float* w = norm_w + (size_t)h * w_stride;
+  // a null weight: the read-outs are only divided by their root mean square
+  const float* w = norm_w ? norm_w + (size_t)h * w_stride : nullptr;
 #pragma unroll 4
   for (int i = lane; i < e; i += 32) {
     const float z = grow[i];
     const float gate_v = gate_sigmoid ? 1.0f / (1.0f + expf(-z)) : silu_f32(z);
-    orow[i] = from_float<TO>(o[i] * inv * w[i] * gate_v);
+    orow[i] = from_float<TO>(o[i] * inv * (w ? w[i] : 1.0f) * gate_v);
   }
 }
 
@@ -434,6 +435,30 @@ extern "C" int cretif_delta_recurrence(const float* prep, int ldp, const float* 
   else
     delta_out_norm_kernel<__nv_bfloat16><<<blocks, 256, 0, st>>>(
         o_raw, gate, ldg, norm_w, eps, (__nv_bfloat16*)out, ldo, H, e, items, 0, 0);
+  return launch_status();
+}
+
+// The per-head norm and gate of read-outs on their own, for other recurrences with a matrix per
+// head (retention.cu): out = o_raw / rms(o_raw) [* norm_w] * gate(gate), a warp per (token, head).
+extern "C" int cretif_heads_out_norm(const float* o_raw, const float* gate, int ldg,
+                                     const float* norm_w, int per_head_weight, int gate_sigmoid,
+                                     float eps, void* out, int out_dt, int ldo, int H, int e, int T,
+                                     void* stream) {
+  if (T <= 0) return kOk;
+  if (H <= 0 || e <= 0 || !o_raw || !gate || ldg < H * e || ldo < H * e) return kBadArgument;
+  const long long items = (long long)T * H;
+  const unsigned blocks = (unsigned)((items + 7) / 8);
+  cudaStream_t st = (cudaStream_t)stream;
+  if (out_dt == kF32)
+    delta_out_norm_kernel<float><<<blocks, 256, 0, st>>>(o_raw, gate, ldg, norm_w, eps,
+                                                         (float*)out, ldo, H, e, items,
+                                                         per_head_weight ? e : 0, gate_sigmoid);
+  else if (out_dt == kBF16)
+    delta_out_norm_kernel<__nv_bfloat16><<<blocks, 256, 0, st>>>(
+        o_raw, gate, ldg, norm_w, eps, (__nv_bfloat16*)out, ldo, H, e, items,
+        per_head_weight ? e : 0, gate_sigmoid);
+  else
+    return kBadDType;
   return launch_status();
 }
 

@@ -15,16 +15,26 @@ namespace cretif {
 template <typename T>
 __global__ void embed_rows_kernel(const T* __restrict__ table, const int* __restrict__ ids,
                                   float* __restrict__ out, int H, int V,
-                                  unsigned int* __restrict__ fault) {
+                                  unsigned int* __restrict__ fault,
+                                  const T* __restrict__ pos_table, const int* __restrict__ tok_pos,
+                                  int P) {
   const int t = blockIdx.x;
   const int id = ids[t];
   float* row = out + (size_t)t * H;
-  if (id < 0 || id >= V) {
+  // a learned vector per position (optional) is added in 32-bit; a position beyond the table
+  // is reported like an id beyond the vocabulary
+  const int pos = pos_table ? tok_pos[t] : 0;
+  if (id < 0 || id >= V || pos < 0 || (pos_table && pos >= P)) {
     if (threadIdx.x == 0) atomicOr(fault, kFaultTokenRange);
     for (int i = threadIdx.x; i < H; i += blockDim.x) row[i] = 0.f;
     return;
   }
   const T* src = table + (size_t)id * H;
+  if (pos_table) {
+    const T* pv = pos_table + (size_t)pos * H;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) row[i] = to_float(src[i]) + to_float(pv[i]);
+    return;
+  }
   for (int i = threadIdx.x; i < H; i += blockDim.x) row[i] = to_float(src[i]);
 }
 
@@ -301,16 +311,19 @@ __global__ void advance_decode_kernel(int* __restrict__ tok_ids, int* __restrict
 using namespace cretif;
 
 extern "C" int cretif_embed_rows(const void* table, int table_dt, const int* ids, float* out,
-                                 int T, int H, int V, unsigned int* fault, void* stream) {
+                                 int T, int H, int V, unsigned int* fault, const void* pos_table,
+                                 const int* tok_pos, int P, void* stream) {
   if (T <= 0) return kOk;
-  if (H <= 0 || V <= 0) return kBadArgument;
+  if (H <= 0 || V <= 0 || (pos_table && (!tok_pos || P <= 0))) return kBadArgument;
   cudaStream_t st = (cudaStream_t)stream;
   const int threads = H >= 256 ? 256 : 64;
   if (table_dt == kF32)
-    embed_rows_kernel<float><<<T, threads, 0, st>>>((const float*)table, ids, out, H, V, fault);
+    embed_rows_kernel<float><<<T, threads, 0, st>>>((const float*)table, ids, out, H, V, fault,
+                                                    (const float*)pos_table, tok_pos, P);
   else if (table_dt == kBF16)
-    embed_rows_kernel<__nv_bfloat16><<<T, threads, 0, st>>>((const __nv_bfloat16*)table, ids, out,
-                                                          H, V, fault);
+    embed_rows_kernel<__nv_bfloat16><<<T, threads, 0, st>>>(
+        (const __nv_bfloat16*)table, ids, out, H, V, fault, (const __nv_bfloat16*)pos_table,
+        tok_pos, P);
   else
     return kBadDType;
   return launch_status();

@@ -115,14 +115,23 @@ def _rows(t: torch.Tensor, name: str) -> int:
 
 
 # ------------------------------------------------------------------ elementwise
-def embed_rows(table, ids, out, fault) -> None:
+def embed_rows(table, ids, out, fault, positions=None, tok_pos=None) -> None:
+    """``positions`` [P, H] (same type as ``table``) with ``tok_pos``: a learned vector per
+    position is added to each token's row."""
     _need(table, "table", dim=2); _need(ids, "ids", torch.int32, 1)
     _need(out, "out", torch.float32, 2); _need(fault, "fault", torch.int32)
     T, (V, H) = ids.numel(), table.shape
     if tuple(out.shape) != (T, H) or not out.is_contiguous() or not table.is_contiguous():
         raise KernelError(f"embed_rows: out must be a contiguous [{T}, {H}] tensor")
+    P = 0
+    if positions is not None:
+        _need(positions, "positions", table.dtype, 2); _need(tok_pos, "tok_pos", torch.int32, 1)
+        P = positions.shape[0]
+        if positions.shape[1] != H or not positions.is_contiguous() or tok_pos.numel() != T:
+            raise KernelError(f"embed_rows: positions must be a contiguous [P, {H}] table with "
+                              "a position per token")
     _check(lib().cretif_embed_rows(_p(table), _dt(table), _p(ids), _p(out), T, H, V, _p(fault),
-                                   _stream()), "embed_rows")
+                                   _p(positions), _p(tok_pos), P, _stream()), "embed_rows")
 
 
 def add_rmsnorm(h, delta, weight, out, eps: float, rows=None, write_h: bool = True) -> None:
@@ -343,6 +352,161 @@ def delta_recurrence(prep, gate, state, cu_seqlens, seq_slot, B: int, H: int, G:
         ctypes.c_longlong(state.stride(0)), _p(cu_seqlens), _p(seq_slot), B, H, G, d, e,
         _p(norm_w), ctypes.c_float(eps), _p(o_raw), _p(out), _dt(out), _rows(out, "out"),
         int(write_state), T, _stream()), "delta_recurrence", kernels=2)
+
+
+# ------------------------------------------------------------------ per-head work, retention
+def headnorm_rope_kv_append(proj, bias, wq, wk, eps: float, cos, sin, pairing: int, rot_dim: int,
+                            tok_pos, tok_seq, seq_slot, nh: int, nkv: int, hd: int, vd: int,
+                            q_out, table=None, kc=None, vc=None, block_tokens: int = 64,
+                            write_cache: bool = True, fault=None) -> None:
+    """``proj`` rows [q (nh hd) | k (nkv hd) | v (nkv vd) | ...] (float32, or the type of
+    ``q_out``): + ``bias``, RMS norm of every q and k head times ``wq`` / ``wk`` (float32 [hd],
+    both None for no norm), rotation of each head's first ``rot_dim`` channels by the position;
+    q to ``q_out`` [T, nh hd], k and v into the block cache."""
+    _need(proj, "proj", dim=2); _need(q_out, "q_out", dim=2)
+    T = proj.shape[0]
+    if proj.dtype not in (torch.float32, q_out.dtype):
+        raise KernelError("headnorm_rope_kv_append: proj is float32 or of q_out's type")
+    n_in = (nh + nkv) * hd + nkv * vd
+    if q_out.shape[0] != T or q_out.shape[1] < nh * hd or proj.shape[1] < n_in:
+        raise KernelError("headnorm_rope_kv_append: proj or q_out too narrow")
+    if bias is not None:
+        _need(bias, "bias", torch.float32, 1)
+        if bias.numel() < n_in or not bias.is_contiguous():
+            raise KernelError("headnorm_rope_kv_append: the bias has a number per q, k and v "
+                              "column")
+    if (wq is None) != (wk is None):
+        raise KernelError("headnorm_rope_kv_append: norm weights for q and k, or for neither")
+    if wq is not None:
+        _need(wq, "wq", torch.float32, 1); _need(wk, "wk", torch.float32, 1)
+        if wq.numel() != hd or wk.numel() != hd:
+            raise KernelError("headnorm_rope_kv_append: a norm weight has head_dim numbers")
+    if rot_dim:
+        _need(cos, "cos", torch.float32, 2); _need(sin, "sin", torch.float32, 2)
+        if cos.shape[1] != rot_dim // 2 or not cos.is_contiguous() or not sin.is_contiguous():
+            raise KernelError("headnorm_rope_kv_append: cos/sin must be contiguous "
+                              "[positions, rot_dim/2]")
+    else:
+        cos = sin = None
+    _need(tok_pos, "tok_pos", torch.int32, 1)
+    if write_cache:
+        _need(tok_seq, "tok_seq", torch.int32, 1); _need(seq_slot, "seq_slot", torch.int32, 1)
+        _need(table, "table", torch.int32, 2)
+        _need(kc, "k cache", q_out.dtype, 4); _need(vc, "v cache", q_out.dtype, 4)
+        if (tuple(kc.shape[1:]) != (nkv, block_tokens, hd) or not kc.is_contiguous()
+                or tuple(vc.shape[1:]) != (nkv, block_tokens, vd) or not vc.is_contiguous()):
+            raise KernelError("headnorm_rope_kv_append: caches must be contiguous [blocks, "
+                              f"{nkv}, {block_tokens}, {hd}] and [..., {vd}]")
+    if fault is None:
+        fault = fault_word(proj.device)
+    _check(lib().cretif_headnorm_rope_kv_append(
+        _p(proj), _rows(proj, "proj"), _dt(proj), _p(bias), _p(wq), _p(wk), ctypes.c_float(eps),
+        _p(cos), _p(sin), pairing, rot_dim, _p(tok_pos), _p(tok_seq), _p(seq_slot), nh, nkv, hd,
+        vd, _p(q_out), _rows(q_out, "q_out"), _dt(q_out), _p(table),
+        table.stride(0) if table is not None else 0, _p(kc), _p(vc), block_tokens,
+        int(write_cache), T, _p(fault), _stream()), "headnorm_rope_kv_append")
+
+
+def gate_heads(o, g, nh: int, vd: int) -> None:
+    """``o[t, h, :] *= sigmoid(g[t, h])``; ``g`` float32 [T, >= nh] (columns of a projection)."""
+    _need(o, "o", dim=2); _need(g, "g", torch.float32, 2)
+    if o.shape[1] < nh * vd or g.shape[1] < nh or g.shape[0] != o.shape[0]:
+        raise KernelError("gate_heads: o holds [tokens, heads*value_dim], g [tokens, heads]")
+    _check(lib().cretif_gate_heads(_p(o), _rows(o, "o"), _dt(o), _p(g), _rows(g, "g"), nh, vd,
+                                   o.shape[0], _stream()), "gate_heads")
+
+
+ACTIVATIONS = {"relu2": 0, "gelu_tanh": 1, "silu": 2}
+
+
+def activation(x, out, kind: str) -> None:
+    """``out = act(x)`` element by element: ``relu2`` (the square of relu), ``gelu_tanh``,
+    ``silu``; ``x`` float32 or of ``out``'s type."""
+    _need(x, "x", dim=2); _need(out, "out", dim=2)
+    if kind not in ACTIVATIONS:
+        raise KernelError(f"activation: {kind!r} is none of {sorted(ACTIVATIONS)}")
+    if x.shape != out.shape or x.dtype not in (torch.float32, out.dtype):
+        raise KernelError("activation: out has x's shape, x is float32 or of out's type")
+    _check(lib().cretif_activation(_p(x), _rows(x, "x"), _dt(x), _p(out), _rows(out, "out"),
+                                   _dt(out), x.shape[0], x.shape[1], ACTIVATIONS[kind],
+                                   _stream()), "activation")
+
+
+def softcap(z, cap: float) -> None:
+    """``z <- cap * tanh(z / cap)`` in place (float32, contiguous)."""
+    _need(z, "z", torch.float32)
+    if not z.is_contiguous():
+        raise KernelError("softcap: z must be contiguous")
+    _check(lib().cretif_softcap(_p(z), ctypes.c_longlong(z.numel()), ctypes.c_float(cap),
+                                _stream()), "softcap")
+
+
+def axpy_rows(h, y, alpha: float) -> None:
+    """``h += alpha * y`` in 32-bit; ``y`` float32 or bfloat16 of ``h``'s shape."""
+    _need(h, "h", torch.float32); _need(y, "y")
+    if y.shape != h.shape or not h.is_contiguous() or not y.is_contiguous():
+        raise KernelError("axpy_rows: y must match h, both contiguous")
+    _check(lib().cretif_axpy_rows(_p(h), _p(y), _dt(y), ctypes.c_float(alpha),
+                                  ctypes.c_longlong(h.numel()), _stream()), "axpy_rows")
+
+
+def retention_prepare(proj, prep, cos, sin, pairing: int, rot_dim: int, tok_pos, H: int, d: int,
+                      k_scale: float) -> None:
+    """Rotate the q and k heads of ``proj`` [T, >= 2Hd] (float32) by position into ``prep``
+    [T, 2Hd]; the rotated k is multiplied by ``k_scale``."""
+    _need(proj, "proj", torch.float32, 2); _need(prep, "prep", torch.float32, 2)
+    if rot_dim:
+        _need(cos, "cos", torch.float32, 2); _need(sin, "sin", torch.float32, 2)
+        if cos.shape[1] != rot_dim // 2 or not cos.is_contiguous() or not sin.is_contiguous():
+            raise KernelError("retention_prepare: cos/sin must be contiguous "
+                              "[positions, rot_dim/2]")
+    else:
+        cos = sin = None
+    _need(tok_pos, "tok_pos", torch.int32, 1)
+    if prep.shape[0] != proj.shape[0]:
+        raise KernelError("retention_prepare: a row of prep per row of proj")
+    _check(lib().cretif_retention_prepare(
+        _p(proj), _rows(proj, "proj"), _p(prep), _rows(prep, "prep"), _p(cos), _p(sin), pairing,
+        rot_dim, _p(tok_pos), H, d, ctypes.c_float(k_scale), proj.shape[0], _stream()),
+        "retention_prepare")
+
+
+def retention_recurrence(prep, v, decay, state, cu_seqlens, seq_slot, B: int, H: int, d: int,
+                         e: int, o_raw, write_state: bool = True) -> None:
+    """``S <- decay_h S + k vᵀ; o = Sᵀ q`` over the step's tokens of every (sequence, head), from
+    and to ``state`` (view [slots, H·d·e] float32); ``prep`` [T, 2Hd] holds q and k, ``v``
+    [T, >= He] the values (float32), ``o_raw`` [T, He] receives the read-outs."""
+    _need(prep, "prep", torch.float32, 2); _need(v, "v", torch.float32, 2)
+    _need(decay, "decay", torch.float32, 1); _need(state, "state", torch.float32, 2)
+    _need(o_raw, "o_raw", torch.float32, 2)
+    T = prep.shape[0]
+    if (state.stride(1) != 1 or state.shape[1] != H * d * e or decay.numel() != H
+            or tuple(o_raw.shape) != (T, H * e) or not o_raw.is_contiguous() or v.shape[0] != T):
+        raise KernelError("retention_recurrence: the sizes do not fit")
+    _check(lib().cretif_retention_recurrence(
+        _p(prep), _rows(prep, "prep"), _p(v), _rows(v, "v"), _p(decay), _p(state),
+        ctypes.c_longlong(state.stride(0)), _p(cu_seqlens), _p(seq_slot), B, H, d, e, _p(o_raw),
+        int(write_state), T, _stream()), "retention_recurrence")
+
+
+def heads_out_norm(o_raw, gate, norm_w, eps: float, out, H: int, e: int,
+                   per_head_weight: bool = False, gate_sigmoid: bool = False) -> None:
+    """``out = o_raw / rms(o_raw) [* norm_w] * gate(gate)`` per (token, head) over ``e``
+    channels; ``norm_w`` None, [e] or [H·e]; the gate is SiLU or the logistic function."""
+    _need(o_raw, "o_raw", torch.float32, 2); _need(gate, "gate", torch.float32, 2)
+    _need(out, "out", dim=2)
+    T = o_raw.shape[0]
+    if (tuple(o_raw.shape) != (T, H * e) or not o_raw.is_contiguous() or gate.shape[0] != T
+            or out.shape[0] != T or out.shape[1] < H * e):
+        raise KernelError("heads_out_norm: the sizes do not fit")
+    if norm_w is not None:
+        _need(norm_w, "norm_w", torch.float32, 1)
+        if norm_w.numel() != (H * e if per_head_weight else e):
+            raise KernelError("heads_out_norm: the weight has e or H·e numbers")
+    _check(lib().cretif_heads_out_norm(
+        _p(o_raw), _p(gate), _rows(gate, "gate"), _p(norm_w), int(per_head_weight),
+        int(gate_sigmoid), ctypes.c_float(eps), _p(out), _dt(out), _rows(out, "out"), H, e, T,
+        _stream()), "heads_out_norm")
 
 
 # ------------------------------------------------------------------ Dynamic Tanh, token shift

@@ -256,11 +256,13 @@ class Engine:
         return ctx, want_rows, int(rows.size)
 
     def step(self, entries: Sequence[Entry], want: Union[str, Sequence[Sequence[int]]] = "last",
-             check: bool = True) -> torch.Tensor:
+             check: bool = True, streams: Optional[list] = None) -> torch.Tensor:
         """Run one step; returns float32 logits ``[wanted, vocab]`` on the device, in the
-        order of ``entries`` and of each entry's wanted places."""
+        order of ``entries`` and of each entry's wanted places.  ``streams``, a list, receives
+        the residual stream ``[tokens, hidden]`` after every layer run (the step then runs
+        eagerly, not from a captured graph)."""
         all_rows = isinstance(want, str) and want == "all"
-        key = self._shape_key(entries, want) if self.step_graphs else None
+        key = self._shape_key(entries, want) if self.step_graphs and streams is None else None
         captured = self._graphs.get(key) if key is not None else None
         if captured is not None:
             # the same step shape has been captured: refresh its indices, replay its kernels
@@ -272,6 +274,8 @@ class Engine:
             self._graphs.move_to_end(key)
         else:
             ctx, want_rows, n_want = self.make_context(entries, want)
+            if streams is not None:
+                ctx.extras["streams"] = streams
 
             def launch():
                 return self.model.forward(ctx, self.cache, None if all_rows else want_rows)

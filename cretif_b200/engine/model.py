@@ -29,6 +29,7 @@ class Branch:
     norm: Optional[Part] = None
     post_norm: Optional[Part] = None
     shift: Optional[Part] = None   # between the norm and the part
+    scale: float = 1.0             # factor on what the branch adds to the stream
 
     def parts(self) -> List[Part]:
         return [p for p in (self.norm, self.shift, self.part, self.post_norm) if p is not None]
@@ -104,7 +105,7 @@ class Model:
                 shift = next(it) if bs.shift is not None else None
                 part = next(it)
                 post = next(it) if bs.post_norm is not None else None
-                branches.append(Branch(bs.role, part, norm, post, shift))
+                branches.append(Branch(bs.role, part, norm, post, shift, float(bs.scale)))
             self.layers.append(Layer(ls.prefix, branches,
                                      lookup_part("arrangement", ls.arrangement)))
         self.final_norm = next(it)
@@ -184,11 +185,24 @@ class Model:
     def forward(self, ctx: StepContext, cache, want_rows: Optional[torch.Tensor]) -> torch.Tensor:
         """Run the scheduled layers on the step's tokens; logits [rows, vocab] float32
         at ``want_rows`` (token indices), or at every token when it is None."""
+        from ..csrc import ops
         h = self.embedding.forward(ctx.tok_ids, ctx)
+        # a schedule entry may ask for the model's input to be added again (a further pass
+        # over a span of layers): the embedding's output is kept for it
+        h_in = h.clone() if any(e.add_input for e in self.spec.schedule) else None
+        streams = ctx.extras.get("streams")      # a list: the stream after every layer run
         pending = None
         for i, entry in enumerate(self.spec.schedule):
             layer = self.layers[entry.layer]
+            if entry.add_input:
+                if pending is not None:
+                    ops.axpy_rows(h, pending.contiguous(), 1.0)
+                    pending = None
+                ctx.extras.pop("stream_copy", None)
+                ops.axpy_rows(h, h_in, 1.0)
             pending = layer.run(layer, h, pending, ctx, self.layer_caches(i, cache))
+            if streams is not None:
+                streams.append(h.clone() if pending is None else h + pending.to(h.dtype))
         if want_rows is not None and want_rows.numel() == 0:
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=h.device)
         if hasattr(self.head, "forward_from_residual"):

@@ -3,7 +3,7 @@ position encodings, heads, and the arrangements that wire them into a block."""
 from .base import (LayerCache, Part, StepContext, build_part, lookup_part, register_part,
                    registered_parts)
 from . import (attention, block, delta_rule, embedding, experts, latent_attention,  # noqa: F401
-               mlp, norm, position, shift)                # (importing registers the parts)
+               mlp, norm, position, retention, shift)                # (importing registers the parts)
 
 __all__ = ["LayerCache", "Part", "StepContext", "build_part", "lookup_part", "register_part",
            "registered_parts"]

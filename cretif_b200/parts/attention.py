@@ -170,11 +170,31 @@ class Attention(Part):
         self.query_gain = params.get("query_gain")
         self.distance_bias = params.get("distance_bias")
         self.bias = self.bias_edges = self.bias_dense = None
-        extras = [k for k in ("head_norm", "query_gain", "distance_bias") if params.get(k)] \
-            + (["value_dim"] if self.vd != self.hd else []) + ([] if self.own_kv else ["own_kv"])
+        self.bias_names = params.get("bias")
+        self.head_gate = params.get("head_gate")
+        # the family that norms head by head without a convolution
+        self.headwise = self.conv is None and bool(
+            self.bias_names or self.head_gate or self.head_norm or self.vd != self.hd)
+        extras = [k for k in ("query_gain", "distance_bias") if params.get(k)] \
+            + ([] if self.own_kv else ["own_kv"]) \
+            + ([] if self.headwise else
+               [k for k in ("head_norm",) if params.get(k)]
+               + (["value_dim"] if self.vd != self.hd else []))
         if self.conv is None and extras:
             raise ValueError(f"attention: {extras} are built for convolved projections "
                              "(give `conv`)")
+        if self.conv is not None and (self.bias_names or self.head_gate):
+            raise ValueError("attention: bias and head_gate are built without a convolution")
+        if self.headwise:
+            if self.qk_norm is not None or self.values_are_keys:
+                raise ValueError("attention: projections normed head by head take no norm over "
+                                 "the whole projection and no keys as values")
+            if self.head_norm is not None and not (self.head_norm.get("q")
+                                                   and self.head_norm.get("k")):
+                raise ValueError("attention: head_norm without a convolution names its two "
+                                 "weights (q, k)")
+            if not 1 <= self.vd <= 512:
+                raise ValueError("attention: value_dim must be in [1, 512]")
         if self.conv is not None:
             if self.head_norm is None or self.qk_norm is not None or self.values_are_keys \
                     or (params.get("position") or {}).get("kind", "none") != "none":
@@ -217,13 +237,34 @@ class Attention(Part):
             out["k_norm"] = (params["qk_norm"]["k"], WeightSpec((kv,), init=(1.0, 0.1)))
         if params.get("sink"):
             out["sink"] = (params["sink"], WeightSpec((params["num_heads"],), init=(0.0, 1.0)))
+        if params.get("bias"):
+            b = params["bias"]
+            out["q_bias"] = (b["q"], WeightSpec((q,), init=(0.0, 0.1)))
+            out["k_bias"] = (b["k"], WeightSpec((kv,), init=(0.0, 0.1)))
+            out["v_bias"] = (b["v"], WeightSpec((vdim,), init=(0.0, 0.1)))
+        hn = params.get("head_norm")
+        if hn and not conv and hn.get("q"):
+            out["q_head_norm"] = (hn["q"], WeightSpec((params["head_dim"],), init=(1.0, 0.1)))
+            out["k_head_norm"] = (hn["k"], WeightSpec((params["head_dim"],), init=(1.0, 0.1)))
+        if params.get("head_gate"):
+            out["head_gate"] = (params["head_gate"],
+                                WeightSpec((params["num_heads"], hidden_size)))
         return out
 
     def load(self, tensors):
         # one product for q, k and v: rows [q | k | v] of the stacked matrix
         stacked = [tensors["q"]] + ([tensors["k"]] if self.own_kv else []) \
             + ([tensors["v"]] if self.own_kv and not self.values_are_keys else [])
+        if self.head_gate:
+            stacked.append(tensors["head_gate"])              # rows [q | k | v | gates]
         self.w_qkv = self._matrix(torch.cat(stacked, dim=0))
+        self.in_bias = self.q_head_w = self.k_head_w = None
+        if self.bias_names:
+            self.in_bias = self._vector32(torch.cat([tensors["q_bias"], tensors["k_bias"],
+                                                     tensors["v_bias"]], dim=0))
+        if "q_head_norm" in tensors:
+            self.q_head_w = self._vector32(tensors["q_head_norm"])
+            self.k_head_w = self._vector32(tensors["k_head_norm"])
         if self.conv is not None:
             taps = [tensors["q_conv"]] + ([tensors["k_conv"], tensors["v_conv"]]
                                           if self.own_kv else [])
@@ -293,10 +334,52 @@ class Attention(Part):
             return None
         return linear_few(o, self.w_o, out_dtype=torch.float32)
 
-    def forward(self, x, ctx, cache, into=None):
+    def _forward_headwise(self, x, ctx, cache, into=None, alpha: float = 1.0):
+        """One product for q|k|v|gates with 32-bit sums, one kernel for bias, head norms,
+        rotation and the cache write, attention, the per-head gate, output product."""
+        from .linear import linear_few, linear_scaled_add
+        kv = cache.kv
+        rot = getattr(self.position, "rotary_table", None)
+        if rot is not None:
+            cos, sin, pairing, rot_dim = rot()
+        elif type(self.position).__name__ == "NoPosition":
+            cos = sin = None
+            pairing = rot_dim = 0
+        else:
+            raise ValueError("attention: projections normed head by head take a rotary position "
+                             "encoding or none")
+        proj = linear_few(x, self.w_qkv, out_dtype=torch.float32)
+        q = torch.empty((ctx.T, self.q_dim), dtype=self.dtype, device=x.device)
+        ops.headnorm_rope_kv_append(
+            proj, self.in_bias, self.q_head_w, self.k_head_w,
+            float(self.head_norm["eps"]) if self.head_norm else 0.0, cos, sin, pairing, rot_dim,
+            ctx.tok_pos, ctx.tok_seq, ctx.seq_slot, self.nh, self.nkv, self.hd, self.vd, q,
+            table=kv.table, kc=kv.k, vc=kv.v, block_tokens=kv.block_tokens,
+            write_cache=cache.writes, fault=ctx.fault)
+        o = torch.empty((ctx.T, self.o_dim), dtype=self.dtype, device=x.device)
+        self.attend(q, o, ctx, kv)
+        if self.head_gate:
+            ops.gate_heads(o, proj[:, self.q_dim + self.kv_dim + self.v_dim:], self.nh, self.vd)
+        if into is not None:
+            linear_scaled_add(o, self.w_o, into, alpha)
+            return None
+        return linear_few(o, self.w_o, out_dtype=torch.float32)
+
+    @property
+    def adds_scaled(self) -> bool:
+        """Whether ``forward`` takes ``into`` and ``alpha`` (adds alpha times its output into
+        the residual stream itself)."""
+        return self.headwise
+
+    def forward(self, x, ctx, cache, into=None, alpha: float = 1.0):
         """``into``: a float32 matrix that the output is added to (the residual stream) instead
         of being returned."""
         from .linear import plain_forced, skinny_max_rows
+        if self.headwise:
+            return self._forward_headwise(x, ctx, cache, into, alpha)
+        if alpha != 1.0:
+            raise ValueError("attention: a factor on the output is built for projections normed "
+                             "head by head")
         if self.conv is not None:
             return self._forward_convolved(x, ctx, cache, into)
         kv = cache.kv
@@ -351,7 +434,7 @@ class Attention(Part):
         """bfloat16.  Few tokens: norm + q|k|v + rotary + cache write in one kernel, attention,
         then the output projection added into ``h``.  Many tokens: the same through the norm's
         kernel and the tensor-core products.  False if the step does not qualify."""
-        if norm is None or self.conv is not None:
+        if norm is None or self.conv is not None or self.headwise:
             return False
         if (ctx.T > FUSED_MAX_TOKENS and self.dtype == torch.bfloat16 and not _force_plain
                 and h.dtype == torch.float32 and h.is_contiguous()):

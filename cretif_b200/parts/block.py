@@ -8,7 +8,7 @@ after the feed-forward (src/model.cu:961-968, 1006-1018).  ``layer.branches`` is
 ordered list of the layer's branches (role, part, norm before it, norm after it) and
 ``caches[k]`` is what branch ``k`` keeps between steps (or ``None``).
 
-``residual``: one branch after the other, ``h += post_norm(part(shift(norm(h))))`` each (a
+``residual``: one branch after the other, ``h += scale * post_norm(part(shift(norm(h))))`` each (a
 shift, where a branch has one, blends each normed row with the row of the token before it).  With a
 mixer and a feed-forward behind a norm each this is the reference's block.  A branch without
 a norm hands its part the stream itself (converted to the part's compute type); a norm after
@@ -52,6 +52,27 @@ def run_residual(layer, h, pending, ctx, caches):
     lowp = extras.pop("stream_copy", None) if extras is not None else None
     for branch, cache in zip(layer.branches, caches):
         part = branch.part
+        scale = float(getattr(branch, "scale", 1.0))
+        if scale != 1.0 and branch.post_norm is None:
+            # a residual multiplier: the part hands back what it would add, or (where it can)
+            # adds alpha times it into the stream inside its last kernel
+            if branch.norm is not None and getattr(branch, "shift", None) is None:
+                x = branch.norm.forward(h, pending)
+            else:
+                if pending is not None:
+                    h.add_(pending)
+                x = (branch.shift.forward(h, branch.norm, ctx, cache.shift_state)
+                     if getattr(branch, "shift", None) is not None else stream_as(h, part.dtype))
+            pending, lowp = None, None
+            if getattr(part, "adds_scaled", False):
+                if branch.role == "mixer":
+                    part.forward(x, ctx, cache, into=h, alpha=scale)
+                else:
+                    part.forward(x, ctx, into=h, alpha=scale)
+                continue
+            y = call_part(branch, x, ctx, cache)
+            ops.axpy_rows(h, y if y.is_contiguous() else y.contiguous(), scale)
+            continue
         if (pending is None and branch.norm is not None and branch.post_norm is None
                 and getattr(branch, "shift", None) is None
                 and hasattr(part, "forward_from_residual")):
@@ -80,6 +101,10 @@ def run_residual(layer, h, pending, ctx, caches):
             x = lowp if lowp is not None and lowp.dtype == part.dtype else stream_as(h, part.dtype)
         y = call_part(branch, x, ctx, cache)
         if branch.post_norm is not None:
+            if scale != 1.0:
+                y = branch.post_norm.forward(y.to(h.dtype).contiguous())
+                ops.axpy_rows(h, y.to(h.dtype).contiguous(), scale)
+                continue
             if hasattr(branch.post_norm, "add_into"):
                 # h += norm(y), 32-bit, one kernel, which also leaves the next reader's copy
                 lowp = branch.post_norm.add_into(h, y, emit=True)

@@ -19,29 +19,44 @@ from .linear import linear
 
 @register_part("embedding", "token_embedding")
 class TokenEmbedding(Part):
-    """params: ``name``; sized by the model's vocabulary (``vocab_size`` is injected)."""
+    """params: ``name``; sized by the model's vocabulary (``vocab_size`` is injected).
+    Optional ``positions`` (``{"name", "rows"}``): a learned vector per position, a table of
+    ``rows`` positions, added to the token's row as it is (32-bit sum)."""
 
     graph_safe = True
 
     @classmethod
     def weight_specs(cls, params, hidden_size):
-        return {"table": (params["name"], WeightSpec((params["vocab_size"], hidden_size)))}
+        out = {"table": (params["name"], WeightSpec((params["vocab_size"], hidden_size)))}
+        pos = params.get("positions")
+        if pos:
+            out["positions"] = (pos["name"], WeightSpec((int(pos["rows"]), hidden_size)))
+        return out
 
     def load(self, tensors):
         self.table = self._matrix(tensors["table"])
+        self.positions = self._matrix(tensors["positions"]) if "positions" in tensors else None
+
+    def prepare(self, max_positions: int) -> None:
+        if self.positions is not None and max_positions > self.positions.shape[0]:
+            raise ValueError(f"the model has {self.positions.shape[0]} learned positions; "
+                             f"sequences of up to {max_positions} tokens were asked for")
 
     def forward(self, ids, ctx):
         h = torch.empty((ids.numel(), self.hidden_size), dtype=torch.float32, device=ids.device)
-        ops.embed_rows(self.table, ids, h, ctx.fault)
+        ops.embed_rows(self.table, ids, h, ctx.fault, positions=self.positions,
+                       tok_pos=ctx.tok_pos if self.positions is not None else None)
         return h
 
     def weight_bytes(self):
-        return self.table.numel() * self.table.element_size()
+        n = self.table.numel() + (self.positions.numel() if self.positions is not None else 0)
+        return n * self.table.element_size()
 
 
 @register_part("head", "linear_head")
 class LinearHead(Part):
-    """params: ``tied`` (share the embedding matrix), ``name``, ``vocab_size``."""
+    """params: ``tied`` (share the embedding matrix), ``name``, ``vocab_size``; optional
+    ``softcap`` c: the logits leave as ``c * tanh(logits / c)``."""
 
     graph_safe = True
 
@@ -57,8 +72,14 @@ class LinearHead(Part):
     def tie(self, embedding: TokenEmbedding) -> None:
         self.weight = embedding.table
 
+    def _capped(self, logits):
+        cap = self.params.get("softcap")
+        if cap and logits.numel():
+            ops.softcap(logits, float(cap))
+        return logits
+
     def forward(self, n, ctx):
-        return linear(n, self.weight, out_dtype=torch.float32)
+        return self._capped(linear(n, self.weight, out_dtype=torch.float32))
 
     def forward_from_residual(self, h, pending, norm, rows, ctx):
         """Few wanted rows, bfloat16: final norm and head product in one kernel; None if the
@@ -73,7 +94,7 @@ class LinearHead(Part):
         logits = torch.empty((R, self.weight.shape[0]), dtype=torch.float32, device=h.device)
         norm_w, eps = rms()
         ops.fused_norm_linear(h, norm_w, eps, self.weight, logits, rows=rows)
-        return logits
+        return self._capped(logits)
 
     def weight_bytes(self):
         if self.params.get("tied") or self.weight is None:

@@ -78,3 +78,14 @@ def linear_few(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype
             ops.fused_linear_x(x, w, out, accumulate)
             return out
     return linear(x, w, out_dtype=out_dtype, out=out, accumulate=accumulate)
+
+
+def linear_scaled_add(x: torch.Tensor, w: torch.Tensor, h: torch.Tensor, alpha: float) -> None:
+    """``h += alpha * x · Wᵀ`` with ``h`` a float32 matrix (the residual stream).  With
+    ``alpha`` 1 the product's kernels add their 32-bit sums into ``h`` themselves; any other
+    factor goes through a 32-bit product and one fused multiply-add per element."""
+    if alpha == 1.0:
+        linear_few(x, w, out=h, accumulate=True)
+        return
+    y = linear_few(x, w, out_dtype=torch.float32)
+    ops.axpy_rows(h, y, float(alpha))

@@ -11,7 +11,7 @@ import torch
 from ..csrc import ops
 from ..weights.loader import WeightSpec
 from .base import Part, register_part
-from .linear import linear, plain_forced, skinny_max_rows as SKINNY_ROWS
+from .linear import linear, linear_scaled_add, plain_forced, skinny_max_rows as SKINNY_ROWS
 
 
 @register_part("feed_forward", "gated_mlp")
@@ -100,3 +100,48 @@ class GatedMLP(Part):
 
     def weight_bytes(self):
         return (self.w_gate_up.numel() + self.w_down.numel()) * self.w_down.element_size()
+
+
+@register_part("feed_forward", "dense_mlp")
+class DenseMLP(Part):
+    """The feed-forward without a gate: ``down(act(up(x)))``, no bias.  params:
+    ``intermediate_size``, ``activation`` ("relu2": the square of relu; "gelu_tanh"; "silu"),
+    ``names`` (up, down).  The activation reads the product's 32-bit sums."""
+
+    graph_safe = True
+    adds_scaled = True
+
+    def __init__(self, params, hidden_size, dtype, device):
+        super().__init__(params, hidden_size, dtype, device)
+        self.inter = int(params["intermediate_size"])
+        self.activation = params.get("activation", "relu2")
+        if self.activation not in ops.ACTIVATIONS:
+            raise ValueError(f"dense_mlp: activation {self.activation!r} has no kernel "
+                             f"(there are {sorted(ops.ACTIVATIONS)})")
+
+    @classmethod
+    def weight_specs(cls, params, hidden_size):
+        I, n = params["intermediate_size"], params["names"]
+        return {"up": (n["up"], WeightSpec((I, hidden_size))),
+                "down": (n["down"], WeightSpec((hidden_size, I)))}
+
+    def load(self, tensors):
+        self.w_up = self._matrix(tensors["up"])
+        self.w_down = self._matrix(tensors["down"])
+
+    def forward(self, x, ctx, into=None, alpha: float = 1.0):
+        """``into``: a float32 matrix that ``alpha`` times the output is added to (the residual
+        stream) instead of the output being returned."""
+        from .linear import linear_few
+        T = x.shape[0]
+        act = torch.empty((T, self.inter), dtype=self.dtype, device=x.device)
+        up = linear_few(x, self.w_up, out_dtype=torch.float32)
+        ops.activation(up, act, self.activation)
+        if into is not None:
+            linear_scaled_add(act, self.w_down, into, alpha)
+            return None
+        return linear_few(act, self.w_down, out_dtype=torch.float32)
+
+    def weight_bytes(self):
+        return (self.w_up.numel() + self.w_down.numel()) * self.w_down.element_size()
+
