@@ -98,7 +98,7 @@ def mixer_attention(h, W, p, m, eps):
     k = unit(k, eps) * W[p + "k.norm"]
     q = rotate_front(q, m["rot"]["base"], m["rot"]["dims"])
     k = rotate_front(k, m["rot"]["base"], m["rot"]["dims"])
-    vis = window_mask(S, m["mask"]["size"])
+    vis = window_mask(S, (m.get("mask") or {}).get("size", S))     # no mask: every earlier key
     gate = torch.sigmoid(h @ W[p + "g"].T)                   # [S, H]
     out = torch.zeros(S, H, e, dtype=h.dtype)
     for hh in range(H):
