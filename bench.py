@@ -21,7 +21,7 @@ fraction for each); ``prefill_b8`` and ``prefill_b64`` are steps over 8 and 64 p
 ``--dtype float32`` measures the true 32-bit path.
 Every weight plus the cache exceed the L2 cache, so no flush is needed between steps.
 
-    python bench.py --design rigozen|losorax [--design-size s|m] [--layers L]
+    python bench.py --design rigozen|losorax|virorax [--design-size s|m] [--layers L]
 
 measures another thing and leaves the line above as it is: prefill (1 and 8 prompts of 2,048
 tokens) and decode (batch 1, 8, 64 from a context of 2,048) of Rigozen models whose layers
@@ -31,7 +31,10 @@ heads and window, each with a roofline fraction (see design_bench).  ``--design 
 the same for Losorax models (all layers convolved attention with a dense or a routed
 feed-forward, all layers the generalized delta rule, and a mixture in which every second
 attention layer reads its neighbour's keys and values) beside Llama without a window and
-beside Rigozen's delta-rule layers.
+beside Rigozen's delta-rule layers.  ``--design virorax`` does it for Virorax models (all layers
+attention with biases, head norms, a sink and a gate; all layers retention; a mixture whose
+second half runs twice) beside Llama with the same window and beside Rigozen's delta-rule
+layers.
 """
 from __future__ import annotations
 
@@ -362,6 +365,42 @@ def losorax_configs(z, layers):
     }
 
 
+def virorax_configs(z, layers):
+    """name -> config.json of the models --design virorax measures; the attention rotates half
+    of each head, the retention heads decay over 32 to 2,048 tokens."""
+    att = {"heads": z["heads"], "kv_heads": z["kv"], "dim": z["dim"], "vdim": z["dim"],
+           "scale": z["dim"] ** -0.5, "mask": {"size": z["window"]},
+           "rot": {"base": 250000.0, "dims": z["dim"] // 2}}
+    H = z["d_heads"]
+    ret = {"heads": H, "dim": z["d_dim"], "vdim": z["d_vdim"],
+           "decay": [1.0 - 2.0 ** (-5.0 - 6.0 * h / max(1, H - 1)) for h in range(H)],
+           "rot": {"base": 1000000.0, "dims": z["d_dim"]}}
+    mlp = {"kind": "dense", "ff": z["ff"]}
+    kinds = {"attention": att, "retention": ret}
+
+    def virorax(order, loop=None):
+        cfg = {"architecture": "Virorax", "vocab": z["vocab"], "width": z["width"],
+               "norm": {"eps": 1e-6}, "max_positions": CONTEXT, "residual_mult": 0.7,
+               "logit_softcap": 15.0,
+               "layers": [{"type": k, "mixer": kinds[k], "mlp": mlp} for k in order]}
+        if loop:
+            cfg["loop"] = loop
+        return cfg
+    base = design_configs(z, layers)
+    # as many layer runs as the others have layers: a span in the middle runs twice
+    span = max(1, layers // 4)
+    n = max(1, layers - span)
+    start = max(0, min(n - span, n // 2 - span // 2))
+    order = (["retention", "attention", "attention", "retention"] * layers)[:n]
+    return {
+        "llama": base["llama"], "rigozen delta": base["rigozen delta"],
+        "virorax attention": virorax(["attention"] * layers),
+        "virorax retention": virorax(["retention"] * layers),
+        "virorax mixed, a span twice": virorax(
+            order, {"start": start, "stop": min(n, start + span), "times": 2}),
+    }
+
+
 def design_configs(z, layers):
     """name -> config.json of the models --design measures."""
     att = {"heads": z["heads"], "kv_heads": z["kv"], "dim": z["dim"], "vdim": z["dim"],
@@ -408,7 +447,9 @@ def design_bench(args) -> int:
     pk = peaks()
     T, W, V = PROMPT_LEN, z["width"], z["vocab"]
     rows = {}
-    configs = losorax_configs(z, layers) if args.design == "losorax" else design_configs(z, layers)
+    configs = (losorax_configs(z, layers) if args.design == "losorax"
+               else virorax_configs(z, layers) if args.design == "virorax"
+               else design_configs(z, layers))
     with ClockSampler() as clocks:
         for name, cfg in configs.items():
             tmp = tempfile.mkdtemp(prefix="cretif_design_")
@@ -424,12 +465,25 @@ def design_bench(args) -> int:
                 else T
             kinds = ([l["type"] for l in cfg["layers"]] if "layers" in cfg
                      else ["llama"] * layers)
+            if cfg.get("architecture") == "Virorax":
+                # a span of layers may run several times: products and what is kept count per
+                # run, the tensors once
+                runs = [e.layer for e in engine.spec.schedule]
+                kinds = [cfg["layers"][i]["type"] for i in runs]
+                per_layer = [sum(p.weight_bytes() for br in l.branches for p in br.parts())
+                             / (2 if args.dtype == "bfloat16" else 4)
+                             for l in engine.model.layers]
+                params_run = params + sum(per_layer[i] for i in runs) - sum(per_layer)
+            else:
+                params_run = None
             # routed experts: a token multiplies by `top` of them, a step reads those it uses
             routed = [l["mlp"] for l in cfg.get("layers", [])
                       if (l.get("mlp") or {}).get("kind") == "moe"]
             expert_params = sum(3 * W * m["expert"]["ff"] * m["router"]["experts"] for m in routed)
             active_params = params - expert_params + sum(
                 3 * W * m["expert"]["ff"] * m["router"]["top"] for m in routed)
+            if params_run is not None:
+                active_params = params_run
 
             def read_params(b):
                 return params - expert_params + sum(
@@ -444,6 +498,9 @@ def design_bench(args) -> int:
                 if k == "general_delta":
                     attn_flops += T * z["d_heads"] * 8 * z["d_dim"] * z["d_dim"]
                     kept += 2 * 4 * z["d_heads"] * z["d_dim"] * z["d_dim"]
+                elif k == "retention":          # two multiply-adds a state element and token
+                    attn_flops += T * z["d_heads"] * 4 * z["d_dim"] * z["d_vdim"]
+                    kept += 2 * 4 * z["d_heads"] * z["d_dim"] * z["d_vdim"]
                 elif k == "delta":
                     attn_flops += T * z["d_heads"] * 8 * z["d_dim"] * z["d_vdim"]
                     kept += 2 * 4 * z["d_heads"] * z["d_dim"] * z["d_vdim"]
@@ -574,7 +631,7 @@ def main() -> int:
                     help="skip the per-kernel shares of the decode step")
     ap.add_argument("--unequal", action="store_true",
                     help="prompts of unequal lengths 256..2,048 instead of 2,048 each")
-    ap.add_argument("--design", default=None, choices=["rigozen", "losorax"],
+    ap.add_argument("--design", default=None, choices=["rigozen", "losorax", "virorax"],
                     help="measure this design at real layer sizes beside Llama at the same "
                          "sizes instead of the headline (another JSON line)")
     ap.add_argument("--design-size", default="m", choices=sorted(DESIGN_SIZES))
