@@ -346,14 +346,17 @@ int cretif_axpy_rows(float* h, const void* y, int y_dt, float alpha, long long t
 // Retention (retention.cu).  proj rows (float32): [q (H d) | k (H d) | ...]; prep rows: the
 // rotated q and the rotated k times k_scale.  state points at the first sequence slot's
 // matrices [H, d, e]; state_stride is a slot's size in floats.  o_raw [T, H e] receives the
-// read-outs S^T q after S <- decay_h S + k v^T.
+// read-outs S^T q after S <- decay_h S + k v^T.  form: 0 lets the step's shape choose between
+// the recurrence token by token (1) and 64 tokens at a time (2, refused where the sizes or
+// addresses do not allow 16-byte accesses).
 int cretif_retention_prepare(const float* proj, int ldp, float* prep, int ldo, const float* cos_t,
                              const float* sin_t, int pairing, int rot_dim, const int* tok_pos,
                              int H, int d, float k_scale, int T, void* stream);
 int cretif_retention_recurrence(const float* prep, int ldp, const float* v, int ldv,
                                 const float* decay, float* state, long long state_stride,
                                 const int* cu_seqlens, const int* seq_slot, int B, int H, int d,
-                                int e, float* o_raw, int write_state, int T, void* stream);
+                                int e, float* o_raw, int write_state, int T, int form,
+                                void* stream);
 // out = o_raw / rms(o_raw) per head [* norm_w] * gate(gate): norm_w null, of e numbers, or of
 // H e (per_head_weight); the gate is SiLU or the logistic function (gate_sigmoid).
 int cretif_heads_out_norm(const float* o_raw, const float* gate, int ldg, const float* norm_w,

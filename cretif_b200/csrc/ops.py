@@ -472,10 +472,13 @@ def retention_prepare(proj, prep, cos, sin, pairing: int, rot_dim: int, tok_pos,
 
 
 def retention_recurrence(prep, v, decay, state, cu_seqlens, seq_slot, B: int, H: int, d: int,
-                         e: int, o_raw, write_state: bool = True) -> None:
+                         e: int, o_raw, write_state: bool = True, form: str = "auto") -> None:
     """``S <- decay_h S + k vᵀ; o = Sᵀ q`` over the step's tokens of every (sequence, head), from
     and to ``state`` (view [slots, H·d·e] float32); ``prep`` [T, 2Hd] holds q and k, ``v``
-    [T, >= He] the values (float32), ``o_raw`` [T, He] receives the read-outs."""
+    [T, >= He] the values (float32), ``o_raw`` [T, He] receives the read-outs.  ``form``:
+    ``"token"`` walks the tokens one by one, ``"chunk"`` takes 64 at a time as three matrix
+    products (refused where sizes or addresses rule out 16-byte accesses), ``"auto"`` takes
+    chunks where the step brings 16 tokens a sequence or more and they are allowed."""
     _need(prep, "prep", torch.float32, 2); _need(v, "v", torch.float32, 2)
     _need(decay, "decay", torch.float32, 1); _need(state, "state", torch.float32, 2)
     _need(o_raw, "o_raw", torch.float32, 2)
@@ -486,7 +489,8 @@ def retention_recurrence(prep, v, decay, state, cu_seqlens, seq_slot, B: int, H:
     _check(lib().cretif_retention_recurrence(
         _p(prep), _rows(prep, "prep"), _p(v), _rows(v, "v"), _p(decay), _p(state),
         ctypes.c_longlong(state.stride(0)), _p(cu_seqlens), _p(seq_slot), B, H, d, e, _p(o_raw),
-        int(write_state), T, _stream()), "retention_recurrence")
+        int(write_state), T, {"auto": 0, "token": 1, "chunk": 2}[form], _stream()),
+        "retention_recurrence")
 
 
 def heads_out_norm(o_raw, gate, norm_w, eps: float, out, H: int, e: int,

@@ -2,8 +2,9 @@
 //
 // Per token and head, with state S [d, e] (32-bit, zero at a sequence's start):
 //     S <- decay_h S + k v^T;   o = S^T q
-// so the read-out sees the token's own write.  Two kernels serve any step shape (whole
-// prompts, further chunks at a cached position, single tokens), all arithmetic in 32-bit:
+// so the read-out sees the token's own write.  Three kernels serve any step shape (whole
+// prompts, further chunks at a cached position, single tokens), all arithmetic in 32-bit;
+// the recurrence has a token-by-token form and a form of 64 tokens at a time (further down):
 //
 // * retention_prepare (a CTA per token): the first rot_dim channels of every query and key head
 //   are rotated by the token's position (cos/sin from a 32-bit table), the key is multiplied
@@ -161,6 +162,246 @@ int launch_retention(const float* prep, int ldp, const float* v, int ldv, const 
                                                   write_state);
   return launch_status();
 }
+
+// ---------------------------------------------------------------------------------------------
+// The same recurrence, 64 tokens at a time.  With S0 the state before a chunk of n tokens and
+// g the head's decay,
+//     o_t = g^(t+1) S0^T q_t + sum_{s<=t} g^(t-s) (q_t . k_s) v_s        (t = 0 .. n-1)
+//     S_n = g^n S0 + sum_s g^(n-1-s) k_s v_s^T
+// which are three matrix products a chunk instead of a chain of n dependent steps.  The powers
+// of g come from a table (never a quotient of two powers, so a small g loses nothing).  A CTA
+// owns (sequence, head, EC columns of S) and walks the sequence's chunks; q, k, the scores and
+// its slice of S live in shared memory, all in 32-bit on the FMA pipe.  Rows of q, k and the
+// scores are padded to 4 mod 8 floats so that eight rows' 16-byte loads fall into eight
+// different bank groups.
+constexpr int kRcTokens = 64;
+constexpr int kRcThreads = 256;
+constexpr int kRcScoreLd = kRcTokens + 4;
+
+__device__ __forceinline__ void fma4(float4& a, float s, const float4& v) {
+  a.x = fmaf(s, v.x, a.x);
+  a.y = fmaf(s, v.y, a.y);
+  a.z = fmaf(s, v.z, a.z);
+  a.w = fmaf(s, v.w, a.w);
+}
+__device__ __forceinline__ float dot4(const float4& a, const float4& b, float acc) {
+  acc = fmaf(a.x, b.x, acc);
+  acc = fmaf(a.y, b.y, acc);
+  acc = fmaf(a.z, b.z, acc);
+  return fmaf(a.w, b.w, acc);
+}
+
+__host__ __device__ inline int retention_chunk_ld(int d) {
+  int ld = d;
+  while ((ld & 7) != 4) ++ld;
+  return ld;
+}
+inline size_t retention_chunk_smem(int d, int ec) {
+  return sizeof(float) * (2 * (size_t)kRcTokens * retention_chunk_ld(d) + (size_t)kRcTokens * ec +
+                          (size_t)kRcTokens * kRcScoreLd + (size_t)d * ec + kRcTokens + 4);
+}
+
+template <int EC>
+__global__ void __launch_bounds__(kRcThreads)
+retention_chunked_kernel(const float* __restrict__ prep, int ldp, const float* __restrict__ v,
+                         int ldv, const float* __restrict__ decay, float* __restrict__ state,
+                         size_t state_stride, const int* __restrict__ cu_seqlens,
+                         const int* __restrict__ seq_slot, int H, int d, int e,
+                         float* __restrict__ o_raw, int write_state) {
+  extern __shared__ __align__(16) float smem[];
+  constexpr int C = kRcTokens;
+  constexpr int LP = kRcScoreLd;
+  constexpr int CG = EC / 4;               // groups of four columns
+  constexpr int NR = kRcThreads / CG;      // threads along the rows
+  constexpr int RT = C / NR;               // read-out rows a thread
+  const int tid = threadIdx.x;
+  const int b = blockIdx.x, h = blockIdx.y, col0 = blockIdx.z * EC;
+  const int t0 = cu_seqlens[b], t1 = cu_seqlens[b + 1];
+  if (t1 <= t0) return;
+  const int ldq = retention_chunk_ld(d);
+  const int d4 = d >> 2;
+  float* sQ = smem;                        // [C][ldq]
+  float* sK = sQ + C * ldq;                // [C][ldq]
+  float* sV = sK + C * ldq;                // [C][EC]
+  float* sP = sV + C * EC;                 // [C][LP]
+  float* sS = sP + C * LP;                 // [d][EC]
+  float* pw = sS + d * EC;                 // g^0 .. g^C
+  if (tid <= C) pw[tid] = (float)pow((double)decay[h], (double)tid);
+  float* M = state + (size_t)seq_slot[b] * state_stride + (size_t)h * d * e + col0;
+  for (int idx = tid; idx < d * CG; idx += kRcThreads) {
+    const int i = idx / CG, jg = idx - i * CG;
+    *reinterpret_cast<float4*>(sS + i * EC + 4 * jg) =
+        *reinterpret_cast<const float4*>(M + (size_t)i * e + 4 * jg);
+  }
+  const int tj = tid % CG, tr = tid / CG;
+  const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int c0 = t0; c0 < t1; c0 += C) {
+    const int nt = min(C, t1 - c0);
+    __syncthreads();                       // the chunk before is done with k and v
+    for (int idx = tid; idx < C * d4; idx += kRcThreads) {
+      const int tt = idx / d4, i4 = idx - tt * d4;
+      float4 q4 = zero4, k4 = zero4;
+      if (tt < nt) {
+        const float* row = prep + (size_t)(c0 + tt) * ldp + (size_t)h * d + 4 * i4;
+        q4 = *reinterpret_cast<const float4*>(row);
+        k4 = *reinterpret_cast<const float4*>(row + (size_t)H * d);
+      }
+      *reinterpret_cast<float4*>(sQ + tt * ldq + 4 * i4) = q4;
+      *reinterpret_cast<float4*>(sK + tt * ldq + 4 * i4) = k4;
+    }
+    for (int idx = tid; idx < C * CG; idx += kRcThreads) {
+      const int tt = idx / CG, jg = idx - tt * CG;
+      float4 v4 = zero4;
+      if (tt < nt)
+        v4 = *reinterpret_cast<const float4*>(v + (size_t)(c0 + tt) * ldv + (size_t)h * e + col0 +
+                                              4 * jg);
+      *reinterpret_cast<float4*>(sV + tt * EC + 4 * jg) = v4;
+    }
+    __syncthreads();
+    {
+      // scores: thread (ti, si) owns rows ti + 16 r and keys si + 16 r'; key blocks ahead of the
+      // row block are never computed
+      const int ti = tid >> 4, si = tid & 15;
+      float acc[4][4];
+#pragma unroll
+      for (int r = 0; r < 4; ++r)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) acc[r][c] = 0.f;
+      for (int kk = 0; kk < d; kk += 4) {
+        float4 q4[4], k4[4];
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+          q4[r] = *reinterpret_cast<const float4*>(sQ + (ti + 16 * r) * ldq + kk);
+          k4[r] = *reinterpret_cast<const float4*>(sK + (si + 16 * r) * ldq + kk);
+        }
+#pragma unroll
+        for (int r = 0; r < 4; ++r)
+#pragma unroll
+          for (int c = 0; c <= r; ++c) acc[r][c] = dot4(q4[r], k4[c], acc[r][c]);
+      }
+#pragma unroll
+      for (int r = 0; r < 4; ++r)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          const int t = ti + 16 * r, s = si + 16 * c;
+          sP[t * LP + s] = (c < r || (c == r && si <= ti)) ? acc[r][c] * pw[t - s] : 0.f;
+        }
+    }
+    __syncthreads();
+    {
+      // read-outs: rows tr + NR r, columns 4 tj .. 4 tj + 3
+      float4 accP[RT], accS[RT];
+#pragma unroll
+      for (int r = 0; r < RT; ++r) accP[r] = accS[r] = zero4;
+      const int smax = min(nt, tr + NR * (RT - 1) + 1);
+      for (int s = 0; s < smax; s += 4) {
+        const float4 v0 = *reinterpret_cast<const float4*>(sV + (s + 0) * EC + 4 * tj);
+        const float4 v1 = *reinterpret_cast<const float4*>(sV + (s + 1) * EC + 4 * tj);
+        const float4 v2 = *reinterpret_cast<const float4*>(sV + (s + 2) * EC + 4 * tj);
+        const float4 v3 = *reinterpret_cast<const float4*>(sV + (s + 3) * EC + 4 * tj);
+#pragma unroll
+        for (int r = 0; r < RT; ++r) {
+          const float4 p = *reinterpret_cast<const float4*>(sP + (tr + NR * r) * LP + s);
+          fma4(accP[r], p.x, v0);
+          fma4(accP[r], p.y, v1);
+          fma4(accP[r], p.z, v2);
+          fma4(accP[r], p.w, v3);
+        }
+      }
+      for (int i = 0; i < d; i += 4) {
+        const float4 s0 = *reinterpret_cast<const float4*>(sS + (i + 0) * EC + 4 * tj);
+        const float4 s1 = *reinterpret_cast<const float4*>(sS + (i + 1) * EC + 4 * tj);
+        const float4 s2 = *reinterpret_cast<const float4*>(sS + (i + 2) * EC + 4 * tj);
+        const float4 s3 = *reinterpret_cast<const float4*>(sS + (i + 3) * EC + 4 * tj);
+#pragma unroll
+        for (int r = 0; r < RT; ++r) {
+          const float4 q = *reinterpret_cast<const float4*>(sQ + (tr + NR * r) * ldq + i);
+          fma4(accS[r], q.x, s0);
+          fma4(accS[r], q.y, s1);
+          fma4(accS[r], q.z, s2);
+          fma4(accS[r], q.w, s3);
+        }
+      }
+#pragma unroll
+      for (int r = 0; r < RT; ++r) {
+        const int t = tr + NR * r;
+        if (t < nt) {
+          const float w = pw[t + 1];
+          float4 o;
+          o.x = fmaf(w, accS[r].x, accP[r].x);
+          o.y = fmaf(w, accS[r].y, accP[r].y);
+          o.z = fmaf(w, accS[r].z, accP[r].z);
+          o.w = fmaf(w, accS[r].w, accP[r].w);
+          *reinterpret_cast<float4*>(o_raw + (size_t)(c0 + t) * H * e + (size_t)h * e + col0 +
+                                     4 * tj) = o;
+        }
+      }
+    }
+    if (c0 + C >= t1 && !write_state) break;   // nobody reads the state after the last chunk
+    // the keys take their weights g^(n-1-s) for the state's update (nobody reads k meanwhile)
+    for (int idx = tid; idx < nt * d4; idx += kRcThreads) {
+      const int tt = idx / d4, i4 = idx - tt * d4;
+      const float w = pw[nt - 1 - tt];
+      float4 k4 = *reinterpret_cast<float4*>(sK + tt * ldq + 4 * i4);
+      k4.x *= w; k4.y *= w; k4.z *= w; k4.w *= w;
+      *reinterpret_cast<float4*>(sK + tt * ldq + 4 * i4) = k4;
+    }
+    __syncthreads();
+    {
+      const float gn = pw[nt];
+      for (int ig = tr; ig < d4; ig += NR) {
+        float* srow = sS + (4 * ig) * EC + 4 * tj;
+        float4 a0 = *reinterpret_cast<float4*>(srow);
+        float4 a1 = *reinterpret_cast<float4*>(srow + EC);
+        float4 a2 = *reinterpret_cast<float4*>(srow + 2 * EC);
+        float4 a3 = *reinterpret_cast<float4*>(srow + 3 * EC);
+        a0.x *= gn; a0.y *= gn; a0.z *= gn; a0.w *= gn;
+        a1.x *= gn; a1.y *= gn; a1.z *= gn; a1.w *= gn;
+        a2.x *= gn; a2.y *= gn; a2.z *= gn; a2.w *= gn;
+        a3.x *= gn; a3.y *= gn; a3.z *= gn; a3.w *= gn;
+        for (int s = 0; s < nt; ++s) {
+          const float4 k4 = *reinterpret_cast<const float4*>(sK + s * ldq + 4 * ig);
+          const float4 v4 = *reinterpret_cast<const float4*>(sV + s * EC + 4 * tj);
+          fma4(a0, k4.x, v4);
+          fma4(a1, k4.y, v4);
+          fma4(a2, k4.z, v4);
+          fma4(a3, k4.w, v4);
+        }
+        *reinterpret_cast<float4*>(srow) = a0;
+        *reinterpret_cast<float4*>(srow + EC) = a1;
+        *reinterpret_cast<float4*>(srow + 2 * EC) = a2;
+        *reinterpret_cast<float4*>(srow + 3 * EC) = a3;
+      }
+    }
+  }
+  if (write_state) {
+    __syncthreads();
+    for (int idx = tid; idx < d * CG; idx += kRcThreads) {
+      const int i = idx / CG, jg = idx - i * CG;
+      *reinterpret_cast<float4*>(M + (size_t)i * e + 4 * jg) =
+          *reinterpret_cast<const float4*>(sS + i * EC + 4 * jg);
+    }
+  }
+}
+
+template <int EC>
+int launch_retention_chunked(const float* prep, int ldp, const float* v, int ldv,
+                             const float* decay, float* state, size_t state_stride, const int* cu,
+                             const int* seq_slot, int B, int H, int d, int e, float* o_raw,
+                             int write_state, cudaStream_t st) {
+  const size_t smem = retention_chunk_smem(d, EC);
+  auto kern = retention_chunked_kernel<EC>;
+  if (smem > 48 * 1024) {
+    cudaError_t err =
+        cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (err != cudaSuccess) return (int)err;
+  }
+  kern<<<dim3(B, H, e / EC), kRcThreads, smem, st>>>(prep, ldp, v, ldv, decay, state, state_stride,
+                                                     cu, seq_slot, H, d, e, o_raw, write_state);
+  return launch_status();
+}
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 }  // namespace
 }  // namespace cretif
 
@@ -184,15 +425,41 @@ extern "C" int cretif_retention_recurrence(const float* prep, int ldp, const flo
                                            const float* decay, float* state,
                                            long long state_stride, const int* cu_seqlens,
                                            const int* seq_slot, int B, int H, int d, int e,
-                                           float* o_raw, int write_state, int T, void* stream) {
+                                           float* o_raw, int write_state, int T, int form,
+                                           void* stream) {
   if (B <= 0 || T <= 0) return kOk;
   if (H <= 0 || d <= 0 || e <= 0 || !o_raw || ldp < 2 * H * d || ldv < H * e) return kBadArgument;
+  if (form < 0 || form > 2) return kBadArgument;
   static int sm_count = 0;
   if (!sm_count) {
     int dev = 0;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
     if (sm_count <= 0) sm_count = 148;
+  }
+  cudaStream_t st = (cudaStream_t)stream;
+  // 64 tokens at a time where the step brings a sequence 16 tokens or more on average and the
+  // sizes allow 16-byte accesses throughout; token by token otherwise.
+  if (form == 2 || (form == 0 && (long long)T >= 16LL * B)) {
+    const bool fits = d % 4 == 0 && e % 16 == 0 && ldp % 4 == 0 && ldv % 4 == 0 &&
+                      state_stride % 4 == 0 && aligned16(prep) && aligned16(v) &&
+                      aligned16(state) && aligned16(o_raw) && H <= 65535 &&
+                      retention_chunk_smem(d, 16) <= 220 * 1024;
+    if (fits) {
+      // columns a CTA: as many as divide e and fit, fewer while the chip is not filled twice
+      int ec = e % 64 == 0 ? 64 : e % 32 == 0 ? 32 : 16;
+      while (ec > 16 && (retention_chunk_smem(d, ec) > 220 * 1024 ||
+                         (long long)B * H * (e / ec) < 2LL * sm_count))
+        ec /= 2;
+#define CRETIF_RETC(EC)                                                                        \
+  launch_retention_chunked<EC>(prep, ldp, v, ldv, decay, state, (size_t)state_stride,          \
+                               cu_seqlens, seq_slot, B, H, d, e, o_raw, write_state, st)
+      if (ec == 64) return CRETIF_RETC(64);
+      if (ec == 32) return CRETIF_RETC(32);
+      return CRETIF_RETC(16);
+#undef CRETIF_RETC
+    }
+    if (form == 2) return kBadArgument;
   }
   // R rows a lane (a power of two from 4 to 32, about a quarter of d), P lanes a column
   int R = 4;
@@ -207,7 +474,6 @@ extern "C" int cretif_retention_recurrence(const float* prep, int ldp, const flo
   while ((long long)B * H * ((e + ecols - 1) / ecols) < 2LL * sm_count && ecols * P >= 128 &&
          ecols % 2 == 0)
     ecols /= 2;
-  cudaStream_t st = (cudaStream_t)stream;
 #define CRETIF_RET(RR)                                                                          \
   launch_retention<RR>(prep, ldp, v, ldv, decay, state, (size_t)state_stride, cu_seqlens,        \
                        seq_slot, B, H, d, e, P, ecols, o_raw, write_state, st)

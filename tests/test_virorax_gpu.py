@@ -284,6 +284,66 @@ def test_retention_kernels_in_pieces(H, d, e, rot):
     assert torch.equal(state, before)
 
 
+@pytest.mark.parametrize("H,d,e", [(2, 128, 128), (3, 32, 64), (1, 64, 16), (5, 16, 48),
+                                   (2, 20, 32), (1, 256, 32)])
+def test_retention_sixty_four_tokens_at_a_time(H, d, e):
+    """The chunked form of the recurrence against the recurrence written out, over sequences of
+    unequal length fed in pieces that end before, at and after a chunk's edge, with the state
+    carried from piece to piece; the state it leaves equals the token-by-token form's."""
+    from cretif_b200.csrc import ops
+    g = torch.Generator().manual_seed(11)
+    lens = [331, 64, 129]
+    decay = torch.tensor([0.999, 0.5, 1.0, 0.97, 0.9][:H])
+    seqs = [(torch.randn(n, 2 * H * d, generator=g), torch.randn(n, H * e, generator=g))
+            for n in lens]
+    want = [plain.retention(p[:, :H * d].double().reshape(-1, H, d),
+                            p[:, H * d:].double().reshape(-1, H, d) * d ** -0.5,
+                            v.double().reshape(-1, H, e), decay.double()).reshape(-1, H * e)
+            for p, v in seqs]
+    scale = max(1.0, max(float(w.abs().max()) for w in want))
+    slots = torch.tensor([3, 0, 2], dtype=torch.int32, device="cuda")
+    states = {}
+    for form in ("chunk", "token"):
+        state = torch.zeros(5, H * d * e, device="cuda")
+        state[1] = 7.0
+        at = [0, 0, 0]
+        for cuts in ((63, 64, 1), (2, 0, 64), (65, 0, 64), (1, 0, 0), (200, 0, 0)):
+            live = [i for i, n in enumerate(cuts) if n]
+            prep = torch.cat([seqs[i][0][at[i]:at[i] + cuts[i]] for i in live]).cuda()
+            prep[:, H * d:] *= d ** -0.5
+            v = torch.cat([seqs[i][1][at[i]:at[i] + cuts[i]] for i in live]).cuda()
+            cu = torch.tensor(np.cumsum([0] + [cuts[i] for i in live]), dtype=torch.int32,
+                              device="cuda")
+            o_raw = torch.full((prep.shape[0], H * e), float("nan"), device="cuda")
+            ops.retention_recurrence(prep, v, decay.cuda(), state, cu, slots[live].contiguous(),
+                                     len(live), H, d, e, o_raw, form=form)
+            row = 0
+            for i in live:
+                got = o_raw[row:row + cuts[i]].cpu().double()
+                ref = want[i][at[i]:at[i] + cuts[i]]
+                assert (got - ref).abs().max() <= 2e-5 * scale, (form, cuts, i)
+                row += cuts[i]
+                at[i] += cuts[i]
+        assert at == lens
+        assert bool((state[1] == 7.0).all()) and bool((state[4] == 0.0).all())
+        states[form] = state
+    diff = (states["chunk"] - states["token"]).abs().max()
+    assert diff <= 2e-5 * max(1.0, float(states["token"].abs().max()))
+
+
+def test_the_chunked_form_is_refused_where_it_cannot_run():
+    from cretif_b200.csrc import ops
+    H, d, e, T = 1, 6, 16, 70
+    args = (torch.zeros(T, 2 * H * d, device="cuda"), torch.zeros(T, H * e, device="cuda"),
+            torch.ones(H, device="cuda"), torch.zeros(1, H * d * e, device="cuda"),
+            torch.tensor([0, T], dtype=torch.int32, device="cuda"),
+            torch.zeros(1, dtype=torch.int32, device="cuda"), 1, H, d, e,
+            torch.empty(T, H * e, device="cuda"))
+    with pytest.raises(ops.KernelError):
+        ops.retention_recurrence(*args, form="chunk")
+    ops.retention_recurrence(*args, form="auto")          # takes the other form
+
+
 def test_retention_of_several_sequences_in_one_launch():
     from cretif_b200.csrc import ops
     g = torch.Generator().manual_seed(6)
