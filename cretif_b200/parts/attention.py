@@ -256,8 +256,10 @@ class Attention(Part):
         stacked = [tensors["q"]] + ([tensors["k"]] if self.own_kv else []) \
             + ([tensors["v"]] if self.own_kv and not self.values_are_keys else [])
         if self.head_gate:
-            stacked.append(tensors["head_gate"])              # rows [q | k | v | gates]
-        self.w_qkv = self._matrix(torch.cat(stacked, dim=0))
+            stacked.append(tensors["head_gate"])              # rows [q | k | v | gates | zeros]
+            self.w_qkv = self._stacked(stacked)
+        else:
+            self.w_qkv = self._matrix(torch.cat(stacked, dim=0))
         self.in_bias = self.q_head_w = self.k_head_w = None
         if self.bias_names:
             self.in_bias = self._vector32(torch.cat([tensors["q_bias"], tensors["k_bias"],

@@ -133,6 +133,17 @@ class Part:
         """A weight matrix in the compute dtype on the device (bf16 → f32 is exact)."""
         return t.to(device=self.device, dtype=self.dtype).contiguous()
 
+    def _stacked(self, mats, multiple: int = 8) -> torch.Tensor:
+        """Several matrices over the same input as one (rows one after the other), with zero
+        rows at the end up to a multiple of ``multiple``: the product's result then has rows
+        whose 32-bit and 16-bit forms are both 16-byte aligned, which the tensor-core kernel
+        asks for.  The added columns of the result are read by nobody."""
+        m = torch.cat(list(mats), dim=0)
+        extra = (-m.shape[0]) % multiple
+        if extra:
+            m = torch.cat([m, m.new_zeros((extra, m.shape[1]))], dim=0)
+        return self._matrix(m)
+
     def _vector32(self, t: torch.Tensor) -> torch.Tensor:
         """A per-channel weight in float32: norms are computed in 32-bit."""
         return t.to(device=self.device, dtype=torch.float32).contiguous()

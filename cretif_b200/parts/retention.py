@@ -69,7 +69,7 @@ class Retention(Part):
     def load(self, tensors):
         t = tensors
         # one product: [q | k | v | gate]
-        self.w_in = self._matrix(torch.cat([t["q"], t["k"], t["v"], t["gate"]], dim=0))
+        self.w_in = self._stacked([t["q"], t["k"], t["v"], t["gate"]])
         self.w_o = self._matrix(t["o"])
         self.decay = torch.tensor(self.decay_host, dtype=torch.float32, device=self.device)
         self.position.load({})
@@ -103,7 +103,8 @@ class Retention(Part):
                                  cache.state, ctx.cu_seqlens, ctx.seq_slot, ctx.B, H, d, e,
                                  o_raw, write_state=cache.writes)
         out = torch.empty((T, H * e), dtype=self.dtype, device=x.device)
-        ops.heads_out_norm(o_raw, proj[:, 2 * H * d + H * e:], None, self.eps, out, H, e)
+        ops.heads_out_norm(o_raw, proj[:, 2 * H * d + H * e:2 * H * d + 2 * H * e], None,
+                           self.eps, out, H, e)
         if into is not None:
             linear_scaled_add(out, self.w_o, into, alpha)
             return None
