@@ -168,9 +168,12 @@ int cretif_gemm_skinny_max_rows(void);
 
 // C[M,N] (= or +=) A[M,K] · W[N,K]^T on the tcgen05 tensor cores (TMA + TMEM), bfloat16
 // operands, C bfloat16 or float32 (+= only float32).  bn = 64/128/192/256 picks the tile width,
-// 0 lets the launcher choose.  A wait that expires sets bit 2 of *fault.
+// 0 lets the launcher choose.  The product is multiplied by alpha before it is stored or added;
+// unary (0 none, 1 relu^2, 2 gelu in its tanh form, 3 silu; stores only) is applied to the
+// 32-bit sums before they are rounded.  A wait that expires sets bit 2 of *fault.
 int cretif_gemm_tc(const void* A, const void* W, void* C, int c_dt, int M, int N, int K, int lda,
-                   int ldw, int ldc, int accumulate, int bn, unsigned int* fault, void* stream);
+                   int ldw, int ldc, int accumulate, int bn, float alpha, int unary,
+                   unsigned int* fault, void* stream);
 
 // (For tests that run both.)  Epilogue warps of the tensor-core product: 4 or 8; 0, the default,
 // chooses per launch.  Returns the old setting.

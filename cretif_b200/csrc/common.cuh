@@ -159,6 +159,17 @@ void count_variant(int v);
 // before them (decode_fused.cu owns the switch).
 int dependent_launch_enabled();
 
+// Activations of a feed-forward without a gate: 0 relu(z)^2, 1 gelu (tanh form), 2 silu.
+__device__ __forceinline__ float unary_activation(float z, int kind) {
+  if (kind == 0) {
+    const float r = fmaxf(z, 0.f);
+    return r * r;
+  }
+  if (kind == 1)
+    return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+  return z / (1.0f + expf(-z));
+}
+
 inline int launch_status() {
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : static_cast<int>(e);

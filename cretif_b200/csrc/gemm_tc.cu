@@ -94,6 +94,10 @@ struct TcEpi {
   // tile_group[mt] is the group of row tile mt, *used_m_tiles how many row tiles are in use
   // (the rest of the grid's tiles is left alone); both are written by the kernel before.
   const int* tile_group; int group_rows; const int* used_m_tiles;
+  // kTcStore only: the product is multiplied by alpha (scaled != 0) before it is stored or
+  // added, and passes an activation (unary: 0 none, else 1 + the kind of unary_activation)
+  // before it is stored
+  float alpha; int scaled; int unary;
 };
 
 __device__ __forceinline__ float round_bf16(float x) {
@@ -336,6 +340,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           if (elected) tc::bulk_wait_group_read<1>();       // the slab used two slabs ago is free
           asm volatile("bar.sync %0, 128;" ::"r"(1 + chalf) : "memory");
           unsigned char* slab = mine + (slabs & 1) * L::kSlab;
+          if (ep.scaled) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(ep.alpha * __uint_as_float(r[j]));
+          }
 #pragma unroll
           for (int j = 0; j < 8; ++j)
             *reinterpret_cast<uint4*>(slab + row * 128 + ((j ^ (row & 7)) << 4)) =
@@ -366,6 +374,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
               float v[8];
 #pragma unroll
               for (int e = 0; e < 8; ++e) v[e] = __uint_as_float(r[j + e]);
+              if (ep.scaled) {
+#pragma unroll
+                for (int e = 0; e < 8; ++e) v[e] *= ep.alpha;
+              }
+              if (ep.unary) {
+#pragma unroll
+                for (int e = 0; e < 8; ++e) v[e] = unary_activation(v[e], ep.unary - 1);
+              }
               const int n = n0 + c0 + j;
               if (n + 8 <= N) {
                 if (pre) {
@@ -734,6 +750,10 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
           if (elected) tc::bulk_wait_group_read<1>();
           asm volatile("bar.sync %0, 128;" ::"r"(1 + chalf) : "memory");
           unsigned char* slab = mine + (slabs & 1) * L::kSlab;
+          if (ep.scaled) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(ep.alpha * __uint_as_float(r[j]));
+          }
 #pragma unroll
           for (int j = 0; j < 8; ++j)
             *reinterpret_cast<uint4*>(slab + row * 128 + ((j ^ (row & 7)) << 4)) =
@@ -1106,9 +1126,10 @@ extern "C" void cretif_gemm_tc_stamps(unsigned long long* device_buffer) {
 #endif
 
 extern "C" int cretif_gemm_tc(const void* A, const void* W, void* C, int c_dt, int M, int N, int K,
-                              int lda, int ldw, int ldc, int accumulate, int bn,
-                              unsigned int* fault, void* stream) {
+                              int lda, int ldw, int ldc, int accumulate, int bn, float alpha,
+                              int unary, unsigned int* fault, void* stream) {
   if (M <= 0 || N <= 0) return kOk;
+  if (unary < 0 || unary > 3 || (unary && accumulate)) return kBadArgument;
   if (K <= 0 || K % 8 || lda % 8 || ldw % 8 || lda < K || ldw < K || ldc < N) return kBadArgument;
   if ((M + kTcBM - 1) / kTcBM > 65535) return kBadArgument;
   if (((uintptr_t)A | (uintptr_t)W | (uintptr_t)C) & 15) return kMisaligned;
@@ -1124,6 +1145,7 @@ extern "C" int cretif_gemm_tc(const void* A, const void* W, void* C, int c_dt, i
   }
   TcEpi ep = {};
   ep.C = C; ep.ldc = ldc; ep.accumulate = accumulate;
+  ep.alpha = alpha; ep.scaled = alpha != 1.0f; ep.unary = unary;
   // The float32 add of a large product: two CTAs a tile (see gemm_tc_pair_kernel), as wide as
   // the single-CTA tile would be.
   if (c_dt == kF32 && accumulate && g_tc_pair != 0 && g_tc_bulk_add && (bn == 256 || bn == 192) &&

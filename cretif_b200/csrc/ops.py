@@ -976,8 +976,10 @@ def set_tc_epilogue_warps(n: int) -> int:
     return int(lib().cretif_set_tc_epilogue_warps(int(n)))
 
 
-def gemm_tc(x, w, out, accumulate: bool = False, bn: int = 0) -> None:
-    """out[M,N] (+)= x[M,K] · w[N,K]ᵀ with TMA, tcgen05.mma and a TMEM accumulator."""
+def gemm_tc(x, w, out, accumulate: bool = False, bn: int = 0, alpha: float = 1.0,
+            unary: Optional[str] = None) -> None:
+    """out[M,N] (+)= alpha · x[M,K] · w[N,K]ᵀ with TMA, tcgen05.mma and a TMEM accumulator;
+    ``unary`` (a key of ACTIVATIONS; stores only) is applied to the 32-bit sums."""
     _need(x, "x", torch.bfloat16, 2); _need(w, "w", torch.bfloat16, 2); _need(out, "out", dim=2)
     M, K = x.shape
     N = w.shape[0]
@@ -985,6 +987,8 @@ def gemm_tc(x, w, out, accumulate: bool = False, bn: int = 0) -> None:
         raise KernelError(f"gemm: shapes {tuple(x.shape)} x {tuple(w.shape)}^T -> {tuple(out.shape)}")
     _check(lib().cretif_gemm_tc(_p(x), _p(w), _p(out), _dt(out), M, N, K, _rows(x, "x"),
                                 _rows(w, "w"), _rows(out, "out"), int(accumulate), bn,
+                                ctypes.c_float(alpha),
+                                0 if unary is None else 1 + ACTIVATIONS[unary],
                                 _p(fault_word(x.device)), _stream()), "gemm_tc")
 
 

@@ -82,10 +82,30 @@ def linear_few(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype
 
 def linear_scaled_add(x: torch.Tensor, w: torch.Tensor, h: torch.Tensor, alpha: float) -> None:
     """``h += alpha * x · Wᵀ`` with ``h`` a float32 matrix (the residual stream).  With
-    ``alpha`` 1 the product's kernels add their 32-bit sums into ``h`` themselves; any other
-    factor goes through a 32-bit product and one fused multiply-add per element."""
+    ``alpha`` 1 the product's kernels add their 32-bit sums into ``h`` themselves; with any other
+    factor the tensor-core product scales its sums before it adds them, and the few-row and
+    float32 kernels go through a 32-bit product and one fused multiply-add per element."""
     if alpha == 1.0:
         linear_few(x, w, out=h, accumulate=True)
         return
+    if (x.shape[0] > FEW_ROWS and x.dtype == torch.bfloat16 and not _force_plain
+            and ops.gemm_tc_supported(x, w, h)):
+        ops.gemm_tc(x, w, h, accumulate=True, alpha=float(alpha))   # scaled in the epilogue
+        return
     y = linear_few(x, w, out_dtype=torch.float32)
     ops.axpy_rows(h, y, float(alpha))
+
+
+def linear_activation(x: torch.Tensor, w: torch.Tensor, kind: str, dtype) -> torch.Tensor:
+    """``act(x · Wᵀ)`` in ``dtype``, the activation on the product's 32-bit sums: in the
+    tensor-core product's epilogue where that kernel takes the step, else as a kernel of its
+    own over a 32-bit result."""
+    M = x.shape[0]
+    act = torch.empty((M, w.shape[0]), dtype=dtype, device=x.device)
+    if (M > FEW_ROWS and x.dtype == torch.bfloat16 and not _force_plain
+            and ops.gemm_tc_supported(x, w, act)):
+        ops.gemm_tc(x, w, act, unary=kind)
+        return act
+    up = linear_few(x, w, out_dtype=torch.float32)
+    ops.activation(up, act, kind)
+    return act

@@ -132,11 +132,8 @@ class DenseMLP(Part):
     def forward(self, x, ctx, into=None, alpha: float = 1.0):
         """``into``: a float32 matrix that ``alpha`` times the output is added to (the residual
         stream) instead of the output being returned."""
-        from .linear import linear_few
-        T = x.shape[0]
-        act = torch.empty((T, self.inter), dtype=self.dtype, device=x.device)
-        up = linear_few(x, self.w_up, out_dtype=torch.float32)
-        ops.activation(up, act, self.activation)
+        from .linear import linear_activation, linear_few
+        act = linear_activation(x, self.w_up, self.activation, self.dtype)
         if into is not None:
             linear_scaled_add(act, self.w_down, into, alpha)
             return None

@@ -140,6 +140,45 @@ def test_gemm_tc(ops, tc_epilogue, M, N, K, bn):
     assert fault.item() == 0
 
 
+@pytest.mark.parametrize("M,N,K,bn", [(300, 200, 72, 0), (1000, 960, 576, 192), (513, 576, 1536, 0),
+                                      (2100, 2048, 264, 256)])
+def test_gemm_tc_scales_what_it_adds_and_applies_an_activation(ops, tc_epilogue, M, N, K, bn):
+    """out += alpha x Wᵀ through every epilogue that adds (threads, TMA, two CTAs a tile), and
+    act(x Wᵀ) stored in bfloat16 and float32, against float64."""
+    x, w = rnd(M, K, dtype=torch.bfloat16), rnd(N, K, dtype=torch.bfloat16, seed=1)
+    prod = x.double() @ w.double().T
+    ldc = -(-N // 8) * 8
+    base = rnd(M, ldc, seed=3)
+    fault = ops.fault_word(DEV)
+    fault.zero_()
+    for pair in (0, 1):
+        for bulk in (False, True):
+            old_p, old_b = ops.set_tc_pair(pair), ops.set_tc_bulk_add(bulk)
+            full = base.clone()
+            c = full[:, :N]
+            ops.gemm_tc(x, w, c, accumulate=True, bn=bn, alpha=-0.7)
+            ops.set_tc_pair(old_p); ops.set_tc_bulk_add(old_b)
+            close(c, base[:, :N].double() - 0.7 * prod, 1e-5)
+            assert torch.equal(full[:, N:], base[:, N:])
+    z = prod.float().double()           # the activation reads the product's 32-bit sums
+    want = {"relu2": z.clamp(min=0) ** 2,
+            "gelu_tanh": 0.5 * z * (1 + torch.tanh(0.7978845608028654 * (z + 0.044715 * z ** 3))),
+            "silu": z / (1 + torch.exp(-z))}
+    for kind, ref in want.items():
+        cb = torch.empty((M, ldc), device=DEV, dtype=torch.bfloat16)[:, :N]
+        ops.gemm_tc(x, w, cb, bn=bn, unary=kind)
+        close(cb, ref, 5e-3)
+        cf = torch.empty((M, ldc), device=DEV)[:, :N]
+        ops.gemm_tc(x, w, cf, bn=bn, unary=kind, alpha=0.5)
+        zh = 0.5 * z
+        ref2 = {"relu2": zh.clamp(min=0) ** 2,
+                "gelu_tanh": 0.5 * zh * (1 + torch.tanh(0.7978845608028654 * (zh + 0.044715 * zh ** 3))),
+                "silu": zh / (1 + torch.exp(-zh))}[kind]
+        close(cf, ref2, 2e-5)
+    torch.cuda.synchronize()
+    assert fault.item() == 0
+
+
 @pytest.mark.parametrize("M,N,K,bn", [(256, 256, 64, 256), (1000, 512, 136, 256), (300, 576, 72, 192),
                                       (130, 960, 200, 192), (2100, 2048, 264, 256)])
 def test_gemm_tc_with_two_ctas_on_a_tile(ops, M, N, K, bn):

@@ -156,6 +156,15 @@ def test_small_row_kernels():
     ops.gate_heads(got, gate.cuda()[:, 5:8], 3, 20)
     want = (o.double().reshape(11, 3, 20) * torch.sigmoid(gate[:, 5:8].double())[:, :, None])
     assert (got.cpu().double() - want.reshape(11, 60)).abs().max() < 1e-6
+    # bfloat16 rows inside a wider buffer: heads of 24 go eight channels a thread, of 20 one
+    for vd in (24, 20):
+        ob = torch.randn(11, 3 * vd + 8, generator=g).bfloat16()
+        buf = ob.cuda()
+        ops.gate_heads(buf[:, :3 * vd], gate.cuda()[:, 5:8], 3, vd)
+        want = (ob[:, :3 * vd].double().reshape(11, 3, vd)
+                * torch.sigmoid(gate[:, 5:8].double())[:, :, None]).reshape(11, 3 * vd)
+        assert ((buf[:, :3 * vd].cpu().double() - want).abs() <= 2.0 ** -8 * want.abs()).all()
+        assert torch.equal(buf[:, 3 * vd:].cpu(), ob[:, 3 * vd:])
 
 
 def _cache_for(positions, nkv, hd, dtype, bt=64):
