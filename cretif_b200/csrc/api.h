@@ -264,10 +264,11 @@ int cretif_attn_decode_mma_bias(const void* q, int ldq, void* out, int ldo, cons
 
 // Fused decode projections (see decode_fused.cu).  H is the float32 residual stream; when it
 // is given, x = bf16(rmsnorm(H[rows])) is computed in the kernel, else X (bfloat16) is read.
+// cretif_fused_linear stores or adds alpha times the product; unary as in cretif_gemm_tc.
 int cretif_fused_linear(const void* X, int ldx, const float* H, const float* norm_w,
                         const int* rows, float eps, const void* W, int ldw, void* C, int c_dt,
-                        int ldc, int accumulate, int M, int N, int K, unsigned int* fault,
-                        void* stream);
+                        int ldc, int accumulate, float alpha, int unary, int M, int N, int K,
+                        unsigned int* fault, void* stream);
 int cretif_fused_qkv_rope(const float* H, const float* norm_w, float eps, const void* Wqkv, int ldw,
                           void* Q, int ldq, const float* cos_t, const float* sin_t, int pairing,
                           int nh, int nkv, int hd, const int* tok_pos, const int* tok_seq,

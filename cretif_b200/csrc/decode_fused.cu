@@ -198,10 +198,12 @@ using namespace cretif;
 // out (+)= norm(h[rows]) · W^T  or  x · W^T, plain epilogue.
 extern "C" int cretif_fused_linear(const void* X, int ldx, const float* H, const float* norm_w,
                                    const int* rows, float eps, const void* W, int ldw, void* C,
-                                   int c_dt, int ldc, int accumulate, int M, int N, int K,
-                                   unsigned int* fault, void* stream) {
+                                   int c_dt, int ldc, int accumulate, float alpha, int unary,
+                                   int M, int N, int K, unsigned int* fault, void* stream) {
   if (M <= 0 || N <= 0) return kOk;
+  if (unary < 0 || unary > 3 || (unary && accumulate)) return kBadArgument;
   FusedParams p = {};
+  p.alpha = alpha; p.scaled = alpha != 1.0f; p.unary = unary;
   p.W = (const __nv_bfloat16*)W; p.M = M; p.N = N; p.K = K; p.ldw = ldw;
   p.X = (const __nv_bfloat16*)X; p.ldx = ldx; p.H = H; p.norm_w = norm_w; p.rows = rows;
   p.eps = eps; p.C = C; p.ldc = ldc; p.c_dt = c_dt; p.accumulate = accumulate; p.fault = fault;

@@ -68,6 +68,8 @@ struct FusedParams {
   // epilogue plain
   void* C;
   int ldc, c_dt, accumulate;
+  float alpha;              // scaled != 0: the product times alpha is what is stored or added
+  int scaled, unary;        // unary: 0 none, else 1 + the kind of unary_activation (stores only)
   // epilogue rope
   __nv_bfloat16* Q;         // [M, nh*hd]
   int ldq;
@@ -205,6 +207,8 @@ __device__ __forceinline__ void finish_tile(const FusedParams& p, int tile,
       float sum = 0.f;
 #pragma unroll
       for (int w = 0; w < kFuWarps; ++w) sum += red[w][rr][m];
+      if (p.scaled) sum *= p.alpha;
+      if (p.unary) sum = unary_activation(sum, p.unary - 1);
       if (p.c_dt == kF32) {
         float* out = reinterpret_cast<float*>(p.C) + (size_t)m * p.ldc + n;
         if (p.accumulate) sum += ahead.old[it];

@@ -1176,8 +1176,8 @@ def fused_norm_linear(h, norm_w, eps: float, w, out, rows=None, accumulate: bool
         raise KernelError("fused_norm_linear: shapes do not fit")
     _check(lib().cretif_fused_linear(None, 0, _p(h), _p(norm_w), _p(rows), ctypes.c_float(eps),
                                      _p(w), _rows(w, "w"), _p(out), _dt(out), _rows(out, "out"),
-                                     int(accumulate), M, N, K, _p(fault_word(h.device)),
-                                     _stream()), "fused_norm_linear")
+                                     int(accumulate), ctypes.c_float(1.0), 0, M, N, K,
+                                     _p(fault_word(h.device)), _stream()), "fused_norm_linear")
 
 
 def fused_linear_add(x, w, h) -> None:
@@ -1189,13 +1189,16 @@ def fused_linear_add(x, w, h) -> None:
     if w.shape[1] != K or tuple(h.shape) != (M, N):
         raise KernelError("fused_linear_add: shapes do not fit")
     _check(lib().cretif_fused_linear(_p(x), _rows(x, "x"), None, None, None, ctypes.c_float(0.0),
-                                     _p(w), _rows(w, "w"), _p(h), F32, _rows(h, "h"), 1, M, N, K,
+                                     _p(w), _rows(w, "w"), _p(h), F32, _rows(h, "h"), 1,
+                                     ctypes.c_float(1.0), 0, M, N, K,
                                      _p(fault_word(h.device)), _stream()), "fused_linear_add")
 
 
-def fused_linear_x(x, w, out, accumulate: bool = False) -> None:
-    """out (+)= x · wᵀ with the few-token kernels (x bfloat16; out bfloat16, or float32 which may
-    be added to)."""
+def fused_linear_x(x, w, out, accumulate: bool = False, alpha: float = 1.0,
+                   unary: Optional[str] = None) -> None:
+    """out (+)= alpha · x · wᵀ with the few-token kernels (x bfloat16; out bfloat16, or float32
+    which may be added to); ``unary`` (a key of ACTIVATIONS; stores only) is applied to the
+    32-bit sums."""
     _need(x, "x", torch.bfloat16, 2); _need(w, "w", torch.bfloat16, 2); _need(out, "out", dim=2)
     M, K = x.shape
     N = w.shape[0]
@@ -1203,8 +1206,9 @@ def fused_linear_x(x, w, out, accumulate: bool = False) -> None:
         raise KernelError("fused_linear_x: shapes do not fit")
     _check(lib().cretif_fused_linear(_p(x), _rows(x, "x"), None, None, None, ctypes.c_float(0.0),
                                      _p(w), _rows(w, "w"), _p(out), _dt(out), _rows(out, "out"),
-                                     int(accumulate), M, N, K, _p(fault_word(x.device)),
-                                     _stream()), "fused_linear_x")
+                                     int(accumulate), ctypes.c_float(alpha),
+                                     0 if unary is None else 1 + ACTIVATIONS[unary], M, N, K,
+                                     _p(fault_word(x.device)), _stream()), "fused_linear_x")
 
 
 def fused_gate_up_silu_x(x, w_gu, act, block: int = 0) -> None:

@@ -61,17 +61,23 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = 
 FEW_ROWS = 64
 
 
+def _few_rows(x: torch.Tensor, w: torch.Tensor) -> bool:
+    """Whether the few-token kernels take this product."""
+    from .attention import fused_steps_enabled
+    M, K = x.shape
+    return (0 < M <= FEW_ROWS and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
+            and not _force_plain and fused_steps_enabled() and x.stride(1) == 1
+            and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0
+            and ops.fused_supported(M, K, w, norm=False))
+
+
 def linear_few(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
                out: Optional[torch.Tensor] = None, accumulate: bool = False) -> torch.Tensor:
     """``linear`` for parts that read rows which are already in the compute type: bfloat16
     steps of at most 64 rows take the few-token kernels (weights streamed once through shared
     memory or registers, launched as programmatic dependents), everything else ``linear``."""
-    from .attention import fused_steps_enabled
     M, K = x.shape
-    if (0 < M <= FEW_ROWS and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
-            and not _force_plain and fused_steps_enabled() and x.stride(1) == 1
-            and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0
-            and ops.fused_supported(M, K, w, norm=False)):
+    if _few_rows(x, w):
         if out is None:
             out = torch.empty((M, w.shape[0]), dtype=out_dtype or x.dtype, device=x.device)
         if out.dtype == torch.float32 or not accumulate:
@@ -83,8 +89,9 @@ def linear_few(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype
 def linear_scaled_add(x: torch.Tensor, w: torch.Tensor, h: torch.Tensor, alpha: float) -> None:
     """``h += alpha * x · Wᵀ`` with ``h`` a float32 matrix (the residual stream).  With
     ``alpha`` 1 the product's kernels add their 32-bit sums into ``h`` themselves; with any other
-    factor the tensor-core product scales its sums before it adds them, and the few-row and
-    float32 kernels go through a 32-bit product and one fused multiply-add per element."""
+    factor the tensor-core product and the few-token kernels scale their sums before they add
+    them, and the other kernels go through a 32-bit product and one fused multiply-add per
+    element."""
     if alpha == 1.0:
         linear_few(x, w, out=h, accumulate=True)
         return
@@ -92,19 +99,25 @@ def linear_scaled_add(x: torch.Tensor, w: torch.Tensor, h: torch.Tensor, alpha: 
             and ops.gemm_tc_supported(x, w, h)):
         ops.gemm_tc(x, w, h, accumulate=True, alpha=float(alpha))   # scaled in the epilogue
         return
+    if _few_rows(x, w):
+        ops.fused_linear_x(x, w, h, accumulate=True, alpha=float(alpha))
+        return
     y = linear_few(x, w, out_dtype=torch.float32)
     ops.axpy_rows(h, y, float(alpha))
 
 
 def linear_activation(x: torch.Tensor, w: torch.Tensor, kind: str, dtype) -> torch.Tensor:
     """``act(x · Wᵀ)`` in ``dtype``, the activation on the product's 32-bit sums: in the
-    tensor-core product's epilogue where that kernel takes the step, else as a kernel of its
-    own over a 32-bit result."""
+    epilogue of the tensor-core product or of the few-token kernels where they take the step,
+    else as a kernel of its own over a 32-bit result."""
     M = x.shape[0]
     act = torch.empty((M, w.shape[0]), dtype=dtype, device=x.device)
     if (M > FEW_ROWS and x.dtype == torch.bfloat16 and not _force_plain
             and ops.gemm_tc_supported(x, w, act)):
         ops.gemm_tc(x, w, act, unary=kind)
+        return act
+    if act.dtype == torch.bfloat16 and _few_rows(x, w):
+        ops.fused_linear_x(x, w, act, unary=kind)
         return act
     up = linear_few(x, w, out_dtype=torch.float32)
     ops.activation(up, act, kind)

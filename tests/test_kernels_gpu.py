@@ -275,7 +275,20 @@ def test_fused_norm_linear_and_add(ops, fused_variant, M, N, K):
     base = rnd(M, N, seed=5)
     acc = base.clone()
     ops.fused_linear_add(x, w, acc)
-    close(acc, base.double().cpu() + x.double().cpu() @ w.double().cpu().T, 1e-5)
+    prod = x.double().cpu() @ w.double().cpu().T
+    close(acc, base.double().cpu() + prod, 1e-5)
+    # a factor on what is added; an activation on what is stored
+    acc = base.clone()
+    ops.fused_linear_x(x, w, acc, accumulate=True, alpha=-0.7)
+    close(acc, base.double().cpu() - 0.7 * prod, 1e-5)
+    z = prod.float().double()
+    for kind, ref in (("relu2", z.clamp(min=0) ** 2), ("silu", z / (1 + torch.exp(-z)))):
+        act = torch.empty(M, N, device=DEV, dtype=torch.bfloat16)
+        ops.fused_linear_x(x, w, act, unary=kind)
+        close(act, ref, 5e-3)
+        act32 = torch.empty(M, N, device=DEV)
+        ops.fused_linear_x(x, w, act32, unary=kind)
+        close(act32, ref, 2e-5)
 
 
 @pytest.mark.parametrize("M,I,K", [(1, 8, 64), (8, 1536, 576), (7, 173, 104), (20, 256, 96),
