@@ -15,6 +15,7 @@
 //   lane's slice of q and k padded so that the P slices fall into different banks); a token
 //   costs one P-lane shuffle reduction and no barrier.  The read-outs leave in 32-bit through
 //   shared memory, a chunk at a time.  The state is read once and written once per step.
+// * retention_intra_kernel + retention_carry_kernel: the form of 64 tokens at a time.
 //
 // The read-outs are normed per head and gated by heads_out_norm (delta_rule.cu).
 #include "api.h"
@@ -168,15 +169,20 @@ int launch_retention(const float* prep, int ldp, const float* v, int ldv, const 
 // g the head's decay,
 //     o_t = g^(t+1) S0^T q_t + sum_{s<=t} g^(t-s) (q_t . k_s) v_s        (t = 0 .. n-1)
 //     S_n = g^n S0 + sum_s g^(n-1-s) k_s v_s^T
-// which are three matrix products a chunk instead of a chain of n dependent steps.  The powers
-// of g come from a table (never a quotient of two powers, so a small g loses nothing).  A CTA
-// owns (sequence, head, EC columns of S) and walks the sequence's chunks; q, k, the scores and
-// its slice of S live in shared memory, all in 32-bit on the FMA pipe.  Rows of q, k and the
-// scores are padded to 4 mod 8 floats so that eight rows' 16-byte loads fall into eight
-// different bank groups.
+// which are matrix products instead of a chain of n dependent steps.  The powers of g come
+// from a table (never a quotient of two powers, so a small g loses nothing).  All of it runs in
+// 32-bit on the FMA pipe, with 16-byte shared-memory loads; rows of q, k and the scores are
+// padded to 4 mod 8 floats so that eight rows' loads fall into eight different bank groups.
+//
+// * retention_intra_kernel (a CTA per (chunk, head); the chunks of all sequences at once): the
+//   second term — the decayed, causally masked scores, then their product with v — written to
+//   o_raw.  Nothing here depends on the state, so a long prompt fills the chip.
+// * retention_carry_kernel (a CTA per (sequence, head, EC columns of S)) walks the sequence's
+//   chunks with its slice of S in shared memory: adds the first term to o_raw, then updates S.
 constexpr int kRcTokens = 64;
 constexpr int kRcThreads = 256;
 constexpr int kRcScoreLd = kRcTokens + 4;
+constexpr int kRcSlab = 64;             // columns of v the intra kernel takes at a time
 
 __device__ __forceinline__ void fma4(float4& a, float s, const float4& v) {
   a.x = fmaf(s, v.x, a.x);
@@ -191,26 +197,171 @@ __device__ __forceinline__ float dot4(const float4& a, const float4& b, float ac
   return fmaf(a.w, b.w, acc);
 }
 
+__device__ __forceinline__ void ret_cp16(float* dst, const float* src) {
+  const unsigned a = (unsigned)__cvta_generic_to_shared(dst);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(a), "l"(src) : "memory");
+}
+__device__ __forceinline__ void ret_cp_commit() {
+  asm volatile("cp.async.commit_group;" ::: "memory");
+}
+template <int N>
+__device__ __forceinline__ void ret_cp_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
 __host__ __device__ inline int retention_chunk_ld(int d) {
   int ld = d;
   while ((ld & 7) != 4) ++ld;
   return ld;
 }
-inline size_t retention_chunk_smem(int d, int ec) {
-  return sizeof(float) * (2 * (size_t)kRcTokens * retention_chunk_ld(d) + (size_t)kRcTokens * ec +
-                          (size_t)kRcTokens * kRcScoreLd + (size_t)d * ec + kRcTokens + 4);
+inline size_t retention_intra_smem(int d) {
+  return sizeof(float) * (2 * (size_t)kRcTokens * retention_chunk_ld(d) +
+                          (size_t)kRcTokens * kRcSlab + (size_t)kRcTokens * kRcScoreLd +
+                          kRcTokens + 4);
+}
+inline size_t retention_carry_smem(int d, int ec, int nbuf = 1) {
+  return sizeof(float) * (nbuf * (2 * (size_t)kRcTokens * retention_chunk_ld(d) +
+                                  (size_t)kRcTokens * ec) +
+                          (size_t)d * ec + kRcTokens + 4);
 }
 
-template <int EC>
 __global__ void __launch_bounds__(kRcThreads)
-retention_chunked_kernel(const float* __restrict__ prep, int ldp, const float* __restrict__ v,
-                         int ldv, const float* __restrict__ decay, float* __restrict__ state,
-                         size_t state_stride, const int* __restrict__ cu_seqlens,
-                         const int* __restrict__ seq_slot, int H, int d, int e,
-                         float* __restrict__ o_raw, int write_state) {
+retention_intra_kernel(const float* __restrict__ prep, int ldp, const float* __restrict__ v, int ldv,
+                       const float* __restrict__ decay, const int* __restrict__ cu_seqlens, int B,
+                       int H, int d, int e, float* __restrict__ o_raw) {
   extern __shared__ __align__(16) float smem[];
   constexpr int C = kRcTokens;
   constexpr int LP = kRcScoreLd;
+  const int tid = threadIdx.x;
+  const int h = blockIdx.y;
+  // which sequence's which chunk: the grid has a CTA for every chunk there can be
+  int left = blockIdx.x, c0 = -1, t1 = 0;
+  for (int b = 0; b < B; ++b) {
+    const int s0 = cu_seqlens[b], s1 = cu_seqlens[b + 1];
+    const int chunks = (s1 - s0 + C - 1) / C;
+    if (left < chunks) {
+      c0 = s0 + left * C;
+      t1 = s1;
+      break;
+    }
+    left -= chunks;
+  }
+  if (c0 < 0) return;
+  const int nt = min(C, t1 - c0);
+  const int ldq = retention_chunk_ld(d);
+  const int d4 = d >> 2;
+  float* sQ = smem;                        // [C][ldq]
+  float* sK = sQ + C * ldq;                // [C][ldq]
+  float* sV = sK + C * ldq;                // [C][kRcSlab]
+  float* sP = sV + C * kRcSlab;            // [C][LP]
+  float* pw = sP + C * LP;                 // g^0 .. g^C
+  if (tid <= C) pw[tid] = (float)pow((double)decay[h], (double)tid);
+  const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
+  // q and k of the chunk's tokens, copied asynchronously (all of a thread's copies are under
+  // way at once).  Rows beyond the chunk's last token stay as they are: they reach only scores
+  // of rows that are not stored, or of keys after the row, which are set to zero.
+  for (int idx = tid; idx < nt * d4; idx += kRcThreads) {
+    const int tt = idx / d4, i4 = idx - tt * d4;
+    const float* row = prep + (size_t)(c0 + tt) * ldp + (size_t)h * d + 4 * i4;
+    ret_cp16(sQ + tt * ldq + 4 * i4, row);
+    ret_cp16(sK + tt * ldq + 4 * i4, row + (size_t)H * d);
+  }
+  ret_cp_commit();
+  // a slab of v: rows beyond the last token and columns beyond the slab are zero (a zero score
+  // times whatever lay there must stay zero)
+  auto stage_v = [&](int j0, int width) {
+    for (int idx = tid; idx < C * (kRcSlab / 4); idx += kRcThreads) {
+      const int tt = idx >> 4, jg = idx & 15;
+      float* dst = sV + tt * kRcSlab + 4 * jg;
+      if (tt < nt && 4 * jg < width)
+        ret_cp16(dst, v + (size_t)(c0 + tt) * ldv + (size_t)h * e + j0 + 4 * jg);
+      else
+        *reinterpret_cast<float4*>(dst) = zero4;
+    }
+    ret_cp_commit();
+  };
+  stage_v(0, min(kRcSlab, e));
+  ret_cp_wait<1>();                        // q and k have arrived
+  __syncthreads();
+  const int ti = tid >> 4, si = tid & 15;
+  {
+    // scores: thread (ti, si) owns rows ti + 16 r and keys si + 16 c; key blocks ahead of the
+    // row block are never computed
+    float acc[4][4];
+#pragma unroll
+    for (int r = 0; r < 4; ++r)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) acc[r][c] = 0.f;
+    for (int kk = 0; kk < d; kk += 4) {
+      float4 q4[4], k4[4];
+#pragma unroll
+      for (int r = 0; r < 4; ++r) {
+        q4[r] = *reinterpret_cast<const float4*>(sQ + (ti + 16 * r) * ldq + kk);
+        k4[r] = *reinterpret_cast<const float4*>(sK + (si + 16 * r) * ldq + kk);
+      }
+#pragma unroll
+      for (int r = 0; r < 4; ++r)
+#pragma unroll
+        for (int c = 0; c <= r; ++c) acc[r][c] = dot4(q4[r], k4[c], acc[r][c]);
+    }
+#pragma unroll
+    for (int r = 0; r < 4; ++r)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const int t = ti + 16 * r, s = si + 16 * c;
+        sP[t * LP + s] = (c < r || (c == r && si <= ti)) ? acc[r][c] * pw[t - s] : 0.f;
+      }
+  }
+  // scores times v, 64 columns at a time: rows ti + 16 r, columns 4 si .. 4 si + 3 of the slab
+  for (int j0 = 0; j0 < e; j0 += kRcSlab) {
+    const int width = min(kRcSlab, e - j0);            // a multiple of 4
+    if (j0 > 0) {
+      __syncthreads();                                 // the slab before has been read
+      stage_v(j0, width);
+    }
+    ret_cp_wait<0>();
+    __syncthreads();                                   // the slab and the scores are in place
+    if (4 * si >= width) continue;
+    float4 acc[4];
+#pragma unroll
+    for (int r = 0; r < 4; ++r) acc[r] = zero4;
+    const int smax = min(nt, ti + 49);
+    for (int s = 0; s < smax; s += 4) {
+      const float4 v0 = *reinterpret_cast<const float4*>(sV + (s + 0) * kRcSlab + 4 * si);
+      const float4 v1 = *reinterpret_cast<const float4*>(sV + (s + 1) * kRcSlab + 4 * si);
+      const float4 v2 = *reinterpret_cast<const float4*>(sV + (s + 2) * kRcSlab + 4 * si);
+      const float4 v3 = *reinterpret_cast<const float4*>(sV + (s + 3) * kRcSlab + 4 * si);
+#pragma unroll
+      for (int r = 0; r < 4; ++r) {
+        if (s > ti + 16 * r) continue;                 // keys after the row: the scores are zero
+        const float4 p = *reinterpret_cast<const float4*>(sP + (ti + 16 * r) * LP + s);
+        fma4(acc[r], p.x, v0);
+        fma4(acc[r], p.y, v1);
+        fma4(acc[r], p.z, v2);
+        fma4(acc[r], p.w, v3);
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+      const int t = ti + 16 * r;
+      if (t < nt)
+        *reinterpret_cast<float4*>(o_raw + (size_t)(c0 + t) * H * e + (size_t)h * e + j0 + 4 * si) =
+            acc[r];
+    }
+  }
+}
+
+// Two buffers for q, k and v where they fit (nbuf = 2): a chunk's copies are under way while
+// the chunk before is computed.
+template <int EC>
+__global__ void __launch_bounds__(kRcThreads)
+retention_carry_kernel(const float* __restrict__ prep, int ldp, const float* __restrict__ v, int ldv,
+                       const float* __restrict__ decay, float* __restrict__ state,
+                       size_t state_stride, const int* __restrict__ cu_seqlens,
+                       const int* __restrict__ seq_slot, int H, int d, int e,
+                       float* __restrict__ o_raw, int write_state, int nbuf) {
+  extern __shared__ __align__(16) float smem[];
+  constexpr int C = kRcTokens;
   constexpr int CG = EC / 4;               // groups of four columns
   constexpr int NR = kRcThreads / CG;      // threads along the rows
   constexpr int RT = C / NR;               // read-out rows a thread
@@ -220,11 +371,8 @@ retention_chunked_kernel(const float* __restrict__ prep, int ldp, const float* _
   if (t1 <= t0) return;
   const int ldq = retention_chunk_ld(d);
   const int d4 = d >> 2;
-  float* sQ = smem;                        // [C][ldq]
-  float* sK = sQ + C * ldq;                // [C][ldq]
-  float* sV = sK + C * ldq;                // [C][EC]
-  float* sP = sV + C * EC;                 // [C][LP]
-  float* sS = sP + C * LP;                 // [d][EC]
+  const int buf_floats = 2 * C * ldq + C * EC;   // q [C][ldq] | k [C][ldq] | v [C][EC]
+  float* sS = smem + nbuf * buf_floats;    // [d][EC]
   float* pw = sS + d * EC;                 // g^0 .. g^C
   if (tid <= C) pw[tid] = (float)pow((double)decay[h], (double)tid);
   float* M = state + (size_t)seq_slot[b] * state_stride + (size_t)h * d * e + col0;
@@ -235,79 +383,55 @@ retention_chunked_kernel(const float* __restrict__ prep, int ldp, const float* _
   }
   const int tj = tid % CG, tr = tid / CG;
   const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
-  for (int c0 = t0; c0 < t1; c0 += C) {
+  // Rows beyond a chunk's last token are not copied: of q they reach only read-outs that are
+  // not stored, of k and v nothing (the update stops at the last token).
+  auto stage = [&](int c0, float* buf) {
     const int nt = min(C, t1 - c0);
-    __syncthreads();                       // the chunk before is done with k and v
-    for (int idx = tid; idx < C * d4; idx += kRcThreads) {
+    for (int idx = tid; idx < nt * d4; idx += kRcThreads) {
       const int tt = idx / d4, i4 = idx - tt * d4;
-      float4 q4 = zero4, k4 = zero4;
-      if (tt < nt) {
-        const float* row = prep + (size_t)(c0 + tt) * ldp + (size_t)h * d + 4 * i4;
-        q4 = *reinterpret_cast<const float4*>(row);
-        k4 = *reinterpret_cast<const float4*>(row + (size_t)H * d);
-      }
-      *reinterpret_cast<float4*>(sQ + tt * ldq + 4 * i4) = q4;
-      *reinterpret_cast<float4*>(sK + tt * ldq + 4 * i4) = k4;
+      const float* row = prep + (size_t)(c0 + tt) * ldp + (size_t)h * d + 4 * i4;
+      ret_cp16(buf + tt * ldq + 4 * i4, row);
+      ret_cp16(buf + C * ldq + tt * ldq + 4 * i4, row + (size_t)H * d);
     }
-    for (int idx = tid; idx < C * CG; idx += kRcThreads) {
+    for (int idx = tid; idx < nt * CG; idx += kRcThreads) {
       const int tt = idx / CG, jg = idx - tt * CG;
-      float4 v4 = zero4;
-      if (tt < nt)
-        v4 = *reinterpret_cast<const float4*>(v + (size_t)(c0 + tt) * ldv + (size_t)h * e + col0 +
-                                              4 * jg);
+      ret_cp16(buf + 2 * C * ldq + tt * EC + 4 * jg,
+               v + (size_t)(c0 + tt) * ldv + (size_t)h * e + col0 + 4 * jg);
+    }
+    ret_cp_commit();
+  };
+  stage(t0, smem);
+  int turn = 0;
+  for (int c0 = t0; c0 < t1; c0 += C, ++turn) {
+    const int nt = min(C, t1 - c0);
+    const bool last = c0 + C >= t1;
+    float* sQ = smem + (nbuf == 2 ? (turn & 1) * buf_floats : 0);
+    float* sK = sQ + C * ldq;
+    float* sV = sK + C * ldq;
+    ret_cp_wait<0>();
+    // v takes the weight g^(n-1-s) it has in the state's update (each thread the pieces it
+    // copied itself; the read-out does not use v)
+    for (int idx = tid; idx < nt * CG; idx += kRcThreads) {
+      const int tt = idx / CG, jg = idx - tt * CG;
+      const float w = pw[nt - 1 - tt];
+      float4 v4 = *reinterpret_cast<float4*>(sV + tt * EC + 4 * jg);
+      v4.x *= w; v4.y *= w; v4.z *= w; v4.w *= w;
       *reinterpret_cast<float4*>(sV + tt * EC + 4 * jg) = v4;
     }
-    __syncthreads();
+    __syncthreads();                       // the chunk is in place; the chunk before is done
+    if (nbuf == 2 && !last) stage(c0 + C, smem + ((turn + 1) & 1) * buf_floats);
     {
-      // scores: thread (ti, si) owns rows ti + 16 r and keys si + 16 r'; key blocks ahead of the
-      // row block are never computed
-      const int ti = tid >> 4, si = tid & 15;
-      float acc[4][4];
+      // what the state before the chunk gives every row: rows tr + NR r, columns 4 tj .. + 3
+      float4 acc[RT], old[RT];
 #pragma unroll
-      for (int r = 0; r < 4; ++r)
-#pragma unroll
-        for (int c = 0; c < 4; ++c) acc[r][c] = 0.f;
-      for (int kk = 0; kk < d; kk += 4) {
-        float4 q4[4], k4[4];
-#pragma unroll
-        for (int r = 0; r < 4; ++r) {
-          q4[r] = *reinterpret_cast<const float4*>(sQ + (ti + 16 * r) * ldq + kk);
-          k4[r] = *reinterpret_cast<const float4*>(sK + (si + 16 * r) * ldq + kk);
-        }
-#pragma unroll
-        for (int r = 0; r < 4; ++r)
-#pragma unroll
-          for (int c = 0; c <= r; ++c) acc[r][c] = dot4(q4[r], k4[c], acc[r][c]);
+      for (int r = 0; r < RT; ++r) {
+        acc[r] = zero4;
+        const int t = tr + NR * r;
+        old[r] = t < nt ? __ldcg(reinterpret_cast<const float4*>(
+                              o_raw + (size_t)(c0 + t) * H * e + (size_t)h * e + col0 + 4 * tj))
+                        : zero4;
       }
-#pragma unroll
-      for (int r = 0; r < 4; ++r)
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          const int t = ti + 16 * r, s = si + 16 * c;
-          sP[t * LP + s] = (c < r || (c == r && si <= ti)) ? acc[r][c] * pw[t - s] : 0.f;
-        }
-    }
-    __syncthreads();
-    {
-      // read-outs: rows tr + NR r, columns 4 tj .. 4 tj + 3
-      float4 accP[RT], accS[RT];
-#pragma unroll
-      for (int r = 0; r < RT; ++r) accP[r] = accS[r] = zero4;
-      const int smax = min(nt, tr + NR * (RT - 1) + 1);
-      for (int s = 0; s < smax; s += 4) {
-        const float4 v0 = *reinterpret_cast<const float4*>(sV + (s + 0) * EC + 4 * tj);
-        const float4 v1 = *reinterpret_cast<const float4*>(sV + (s + 1) * EC + 4 * tj);
-        const float4 v2 = *reinterpret_cast<const float4*>(sV + (s + 2) * EC + 4 * tj);
-        const float4 v3 = *reinterpret_cast<const float4*>(sV + (s + 3) * EC + 4 * tj);
-#pragma unroll
-        for (int r = 0; r < RT; ++r) {
-          const float4 p = *reinterpret_cast<const float4*>(sP + (tr + NR * r) * LP + s);
-          fma4(accP[r], p.x, v0);
-          fma4(accP[r], p.y, v1);
-          fma4(accP[r], p.z, v2);
-          fma4(accP[r], p.w, v3);
-        }
-      }
+#pragma unroll 2
       for (int i = 0; i < d; i += 4) {
         const float4 s0 = *reinterpret_cast<const float4*>(sS + (i + 0) * EC + 4 * tj);
         const float4 s1 = *reinterpret_cast<const float4*>(sS + (i + 1) * EC + 4 * tj);
@@ -316,10 +440,10 @@ retention_chunked_kernel(const float* __restrict__ prep, int ldp, const float* _
 #pragma unroll
         for (int r = 0; r < RT; ++r) {
           const float4 q = *reinterpret_cast<const float4*>(sQ + (tr + NR * r) * ldq + i);
-          fma4(accS[r], q.x, s0);
-          fma4(accS[r], q.y, s1);
-          fma4(accS[r], q.z, s2);
-          fma4(accS[r], q.w, s3);
+          fma4(acc[r], q.x, s0);
+          fma4(acc[r], q.y, s1);
+          fma4(acc[r], q.z, s2);
+          fma4(acc[r], q.w, s3);
         }
       }
 #pragma unroll
@@ -327,26 +451,18 @@ retention_chunked_kernel(const float* __restrict__ prep, int ldp, const float* _
         const int t = tr + NR * r;
         if (t < nt) {
           const float w = pw[t + 1];
-          float4 o;
-          o.x = fmaf(w, accS[r].x, accP[r].x);
-          o.y = fmaf(w, accS[r].y, accP[r].y);
-          o.z = fmaf(w, accS[r].z, accP[r].z);
-          o.w = fmaf(w, accS[r].w, accP[r].w);
+          float4 o = old[r];
+          o.x = fmaf(w, acc[r].x, o.x);
+          o.y = fmaf(w, acc[r].y, o.y);
+          o.z = fmaf(w, acc[r].z, o.z);
+          o.w = fmaf(w, acc[r].w, o.w);
           *reinterpret_cast<float4*>(o_raw + (size_t)(c0 + t) * H * e + (size_t)h * e + col0 +
                                      4 * tj) = o;
         }
       }
     }
-    if (c0 + C >= t1 && !write_state) break;   // nobody reads the state after the last chunk
-    // the keys take their weights g^(n-1-s) for the state's update (nobody reads k meanwhile)
-    for (int idx = tid; idx < nt * d4; idx += kRcThreads) {
-      const int tt = idx / d4, i4 = idx - tt * d4;
-      const float w = pw[nt - 1 - tt];
-      float4 k4 = *reinterpret_cast<float4*>(sK + tt * ldq + 4 * i4);
-      k4.x *= w; k4.y *= w; k4.z *= w; k4.w *= w;
-      *reinterpret_cast<float4*>(sK + tt * ldq + 4 * i4) = k4;
-    }
-    __syncthreads();
+    if (last && !write_state) break;       // nobody reads the state after the last chunk
+    __syncthreads();                       // everybody has read the old state
     {
       const float gn = pw[nt];
       for (int ig = tr; ig < d4; ig += NR) {
@@ -359,6 +475,7 @@ retention_chunked_kernel(const float* __restrict__ prep, int ldp, const float* _
         a1.x *= gn; a1.y *= gn; a1.z *= gn; a1.w *= gn;
         a2.x *= gn; a2.y *= gn; a2.z *= gn; a2.w *= gn;
         a3.x *= gn; a3.y *= gn; a3.z *= gn; a3.w *= gn;
+#pragma unroll 4
         for (int s = 0; s < nt; ++s) {
           const float4 k4 = *reinterpret_cast<const float4*>(sK + s * ldq + 4 * ig);
           const float4 v4 = *reinterpret_cast<const float4*>(sV + s * EC + 4 * tj);
@@ -373,6 +490,10 @@ retention_chunked_kernel(const float* __restrict__ prep, int ldp, const float* _
         *reinterpret_cast<float4*>(srow + 3 * EC) = a3;
       }
     }
+    if (nbuf != 2 && !last) {
+      __syncthreads();                     // the one buffer has been read
+      stage(c0 + C, smem);
+    }
   }
   if (write_state) {
     __syncthreads();
@@ -385,19 +506,38 @@ retention_chunked_kernel(const float* __restrict__ prep, int ldp, const float* _
 }
 
 template <int EC>
-int launch_retention_chunked(const float* prep, int ldp, const float* v, int ldv,
-                             const float* decay, float* state, size_t state_stride, const int* cu,
-                             const int* seq_slot, int B, int H, int d, int e, float* o_raw,
-                             int write_state, cudaStream_t st) {
-  const size_t smem = retention_chunk_smem(d, EC);
-  auto kern = retention_chunked_kernel<EC>;
+int launch_retention_carry(const float* prep, int ldp, const float* v, int ldv, const float* decay,
+                           float* state, size_t state_stride, const int* cu, const int* seq_slot,
+                           int B, int H, int d, int e, float* o_raw, int write_state,
+                           cudaStream_t st) {
+  const int nbuf = retention_carry_smem(d, EC, 2) <= 220 * 1024 ? 2 : 1;
+  const size_t smem = retention_carry_smem(d, EC, nbuf);
+  auto kern = retention_carry_kernel<EC>;
   if (smem > 48 * 1024) {
     cudaError_t err =
         cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (err != cudaSuccess) return (int)err;
   }
   kern<<<dim3(B, H, e / EC), kRcThreads, smem, st>>>(prep, ldp, v, ldv, decay, state, state_stride,
-                                                     cu, seq_slot, H, d, e, o_raw, write_state);
+                                                     cu, seq_slot, H, d, e, o_raw, write_state,
+                                                     nbuf);
+  return launch_status();
+}
+
+int launch_retention_intra(const float* prep, int ldp, const float* v, int ldv, const float* decay,
+                           const int* cu, int B, int T, int H, int d, int e, float* o_raw,
+                           cudaStream_t st) {
+  const size_t smem = retention_intra_smem(d);
+  if (smem > 48 * 1024) {
+    cudaError_t err = cudaFuncSetAttribute(
+        retention_intra_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (err != cudaSuccess) return (int)err;
+  }
+  // every sequence has at most one chunk that is not full
+  const long long chunks = (long long)T / kRcTokens + B;
+  if (chunks > 0x7fffffffLL) return kBadArgument;
+  retention_intra_kernel<<<dim3((unsigned)chunks, H), kRcThreads, smem, st>>>(
+      prep, ldp, v, ldv, decay, cu, B, H, d, e, o_raw);
   return launch_status();
 }
 
@@ -444,16 +584,20 @@ extern "C" int cretif_retention_recurrence(const float* prep, int ldp, const flo
     const bool fits = d % 4 == 0 && e % 16 == 0 && ldp % 4 == 0 && ldv % 4 == 0 &&
                       state_stride % 4 == 0 && aligned16(prep) && aligned16(v) &&
                       aligned16(state) && aligned16(o_raw) && H <= 65535 &&
-                      retention_chunk_smem(d, 16) <= 220 * 1024;
+                      retention_carry_smem(d, 16) <= 220 * 1024 &&
+                      retention_intra_smem(d) <= 220 * 1024;
     if (fits) {
-      // columns a CTA: as many as divide e and fit, fewer while the chip is not filled twice
+      int rc = launch_retention_intra(prep, ldp, v, ldv, decay, cu_seqlens, B, T, H, d, e, o_raw,
+                                      st);
+      if (rc != kOk) return rc;
+      // columns a CTA: as many as divide e and fit, fewer while the chip is not filled
       int ec = e % 64 == 0 ? 64 : e % 32 == 0 ? 32 : 16;
-      while (ec > 16 && (retention_chunk_smem(d, ec) > 220 * 1024 ||
-                         (long long)B * H * (e / ec) < 2LL * sm_count))
+      while (ec > 16 && (retention_carry_smem(d, ec) > 220 * 1024 ||
+                         (long long)B * H * (e / ec) < (long long)sm_count))
         ec /= 2;
 #define CRETIF_RETC(EC)                                                                        \
-  launch_retention_chunked<EC>(prep, ldp, v, ldv, decay, state, (size_t)state_stride,          \
-                               cu_seqlens, seq_slot, B, H, d, e, o_raw, write_state, st)
+  launch_retention_carry<EC>(prep, ldp, v, ldv, decay, state, (size_t)state_stride, cu_seqlens, \
+                             seq_slot, B, H, d, e, o_raw, write_state, st)
       if (ec == 64) return CRETIF_RETC(64);
       if (ec == 32) return CRETIF_RETC(32);
       return CRETIF_RETC(16);
