@@ -1165,8 +1165,10 @@ def set_dependent_launch(on: bool) -> bool:
     return bool(lib().cretif_set_dependent_launch(int(on)))
 
 
-def fused_norm_linear(h, norm_w, eps: float, w, out, rows=None, accumulate: bool = False) -> None:
-    """out (+)= bf16(rmsnorm(h[rows])) · wᵀ in one kernel (decode-sized row counts)."""
+def fused_norm_linear(h, norm_w, eps: float, w, out, rows=None, accumulate: bool = False,
+                      unary: Optional[str] = None) -> None:
+    """out (+)= bf16(rmsnorm(h[rows])) · wᵀ in one kernel (decode-sized row counts); ``unary``
+    (a key of ACTIVATIONS; stores only) is applied to the 32-bit sums."""
     _need(h, "h", torch.float32, 2); _need(norm_w, "norm weight", torch.float32, 1)
     _need(w, "w", torch.bfloat16, 2); _need(out, "out", dim=2)
     K = h.shape[1]
@@ -1176,7 +1178,8 @@ def fused_norm_linear(h, norm_w, eps: float, w, out, rows=None, accumulate: bool
         raise KernelError("fused_norm_linear: shapes do not fit")
     _check(lib().cretif_fused_linear(None, 0, _p(h), _p(norm_w), _p(rows), ctypes.c_float(eps),
                                      _p(w), _rows(w, "w"), _p(out), _dt(out), _rows(out, "out"),
-                                     int(accumulate), ctypes.c_float(1.0), 0, M, N, K,
+                                     int(accumulate), ctypes.c_float(1.0),
+                                     0 if unary is None else 1 + ACTIVATIONS[unary], M, N, K,
                                      _p(fault_word(h.device)), _stream()), "fused_norm_linear")
 
 

@@ -336,9 +336,10 @@ class Attention(Part):
             return None
         return linear_few(o, self.w_o, out_dtype=torch.float32)
 
-    def _forward_headwise(self, x, ctx, cache, into=None, alpha: float = 1.0):
-        """One product for q|k|v|gates with 32-bit sums, one kernel for bias, head norms,
-        rotation and the cache write, attention, the per-head gate, output product."""
+    def _forward_headwise(self, x, ctx, cache, into=None, alpha: float = 1.0, proj=None):
+        """One product for q|k|v|gates with 32-bit sums (``proj``, where the caller made it
+        already), one kernel for bias, head norms, rotation and the cache write, attention, the
+        per-head gate, output product."""
         from .linear import linear_few, linear_scaled_add
         kv = cache.kv
         rot = getattr(self.position, "rotary_table", None)
@@ -350,15 +351,15 @@ class Attention(Part):
         else:
             raise ValueError("attention: projections normed head by head take a rotary position "
                              "encoding or none")
-        proj = linear_few(x, self.w_qkv, out_dtype=torch.float32)
-        q = torch.empty((ctx.T, self.q_dim), dtype=self.dtype, device=x.device)
+        proj = linear_few(x, self.w_qkv, out_dtype=torch.float32) if proj is None else proj
+        q = torch.empty((ctx.T, self.q_dim), dtype=self.dtype, device=proj.device)
         ops.headnorm_rope_kv_append(
             proj, self.in_bias, self.q_head_w, self.k_head_w,
             float(self.head_norm["eps"]) if self.head_norm else 0.0, cos, sin, pairing, rot_dim,
             ctx.tok_pos, ctx.tok_seq, ctx.seq_slot, self.nh, self.nkv, self.hd, self.vd, q,
             table=kv.table, kc=kv.k, vc=kv.v, block_tokens=kv.block_tokens,
             write_cache=cache.writes, fault=ctx.fault)
-        o = torch.empty((ctx.T, self.o_dim), dtype=self.dtype, device=x.device)
+        o = torch.empty((ctx.T, self.o_dim), dtype=self.dtype, device=proj.device)
         self.attend(q, o, ctx, kv)
         if self.head_gate:
             ops.gate_heads(o, proj[:, self.q_dim + self.kv_dim + self.v_dim:], self.nh, self.vd)
@@ -432,11 +433,20 @@ class Attention(Part):
             return linear_few(o, self.w_o, out_dtype=torch.float32)
         return linear(o, self.w_o, out_dtype=torch.float32)
 
-    def forward_from_residual(self, h, norm, ctx, cache) -> bool:
+    def forward_from_residual(self, h, norm, ctx, cache, alpha: float = 1.0) -> bool:
         """bfloat16.  Few tokens: norm + q|k|v + rotary + cache write in one kernel, attention,
         then the output projection added into ``h``.  Many tokens: the same through the norm's
-        kernel and the tensor-core products.  False if the step does not qualify."""
-        if norm is None or self.conv is not None or self.headwise:
+        kernel and the tensor-core products.  Projections normed head by head: few tokens take
+        the input product that norms the rows in its prologue, and ``alpha`` times the output
+        product is added into ``h``.  False if the step does not qualify."""
+        if norm is not None and self.headwise and self.conv is None:
+            from .linear import normed_linear_few
+            proj = normed_linear_few(h, norm, self.w_qkv, torch.float32)
+            if proj is None:
+                return False
+            self._forward_headwise(None, ctx, cache, into=h, alpha=alpha, proj=proj)
+            return True
+        if norm is None or self.conv is not None or self.headwise or alpha != 1.0:
             return False
         if (ctx.T > FUSED_MAX_TOKENS and self.dtype == torch.bfloat16 and not _force_plain
                 and h.dtype == torch.float32 and h.is_contiguous()):

@@ -55,7 +55,18 @@ def run_residual(layer, h, pending, ctx, caches):
         scale = float(getattr(branch, "scale", 1.0))
         if scale != 1.0 and branch.post_norm is None:
             # a residual multiplier: the part hands back what it would add, or (where it can)
-            # adds alpha times it into the stream inside its last kernel
+            # adds alpha times it into the stream inside its last kernel; a part that reads the
+            # stream itself also applies the norm in its first kernel
+            if (pending is None and branch.norm is not None
+                    and getattr(branch, "shift", None) is None
+                    and getattr(part, "adds_scaled", False)
+                    and hasattr(part, "forward_from_residual")):
+                took = (part.forward_from_residual(h, branch.norm, ctx, cache, alpha=scale)
+                        if branch.role == "mixer"
+                        else part.forward_from_residual(h, branch.norm, ctx, alpha=scale))
+                if took:
+                    lowp = None
+                    continue
             if branch.norm is not None and getattr(branch, "shift", None) is None:
                 x = branch.norm.forward(h, pending)
             else:

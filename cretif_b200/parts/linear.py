@@ -86,6 +86,24 @@ def linear_few(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype
     return linear(x, w, out_dtype=out_dtype, out=out, accumulate=accumulate)
 
 
+def normed_linear_few(h: torch.Tensor, norm, w: torch.Tensor, out_dtype,
+                      unary: Optional[str] = None) -> Optional[torch.Tensor]:
+    """``[act](rmsnorm(h) · Wᵀ)`` by the few-token kernel that norms the residual rows in its
+    own prologue (and rounds them to bfloat16 as the norm's kernel would), or None where the
+    step, the norm or the sizes do not allow it."""
+    from .attention import fused_steps_enabled
+    rms = getattr(norm, "rms_params", None)
+    M, K = h.shape
+    if (rms is None or not 0 < M <= FEW_ROWS or w.dtype != torch.bfloat16 or _force_plain
+            or not fused_steps_enabled() or h.dtype != torch.float32 or not h.is_contiguous()
+            or not ops.fused_supported(M, K, w)):
+        return None
+    norm_w, eps = rms()
+    out = torch.empty((M, w.shape[0]), dtype=out_dtype, device=h.device)
+    ops.fused_norm_linear(h, norm_w, eps, w, out, unary=unary)
+    return out
+
+
 def linear_scaled_add(x: torch.Tensor, w: torch.Tensor, h: torch.Tensor, alpha: float) -> None:
     """``h += alpha * x · Wᵀ`` with ``h`` a float32 matrix (the residual stream).  With
     ``alpha`` 1 the product's kernels add their 32-bit sums into ``h`` themselves; with any other

@@ -139,6 +139,18 @@ class DenseMLP(Part):
             return None
         return linear_few(act, self.w_down, out_dtype=torch.float32)
 
+    def forward_from_residual(self, h, norm, ctx, alpha: float = 1.0) -> bool:
+        """Few tokens in bfloat16: norm, up product and activation in one kernel, the down
+        product adds ``alpha`` times its sums into ``h``.  False if the step does not qualify."""
+        from .linear import normed_linear_few
+        if self.dtype != torch.bfloat16:
+            return False
+        act = normed_linear_few(h, norm, self.w_up, self.dtype, unary=self.activation)
+        if act is None:
+            return False
+        linear_scaled_add(act, self.w_down, h, alpha)
+        return True
+
     def weight_bytes(self):
         return (self.w_up.numel() + self.w_down.numel()) * self.w_down.element_size()
 

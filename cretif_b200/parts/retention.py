@@ -22,7 +22,7 @@ from ..config.spec import PartSpec
 from ..csrc import ops
 from ..weights.loader import WeightSpec
 from .base import Part, build_part, register_part
-from .linear import linear_few, linear_scaled_add
+from .linear import linear_few, linear_scaled_add, normed_linear_few
 
 
 @register_part("mixer", "retention")
@@ -84,6 +84,19 @@ class Retention(Part):
     def forward(self, x, ctx, cache, into=None, alpha: float = 1.0):
         """``into``: a float32 matrix that ``alpha`` times the output is added to (the residual
         stream) instead of the output being returned."""
+        proj = linear_few(x, self.w_in, out_dtype=torch.float32)      # [T, 2Hd + 2He (+ pad)]
+        return self._finish(proj, ctx, cache, into, alpha)
+
+    def forward_from_residual(self, h, norm, ctx, cache, alpha: float = 1.0) -> bool:
+        """Few tokens in bfloat16: the norm runs in the input product's prologue and the output
+        product adds ``alpha`` times its sums into ``h``.  False if the step does not qualify."""
+        proj = normed_linear_few(h, norm, self.w_in, torch.float32)
+        if proj is None:
+            return False
+        self._finish(proj, ctx, cache, h, alpha)
+        return True
+
+    def _finish(self, proj, ctx, cache, into, alpha):
         H, d, e = self.nh, self.hd, self.vd
         T = ctx.T
         rot = getattr(self.position, "rotary_table", None)
@@ -94,7 +107,7 @@ class Retention(Part):
             pairing = rot_dim = 0
         else:
             raise ValueError("retention takes a rotary position encoding or none")
-        proj = linear_few(x, self.w_in, out_dtype=torch.float32)      # [T, 2Hd + 2He]
+        x = proj
         prep = torch.empty((T, 2 * H * d), dtype=torch.float32, device=x.device)
         ops.retention_prepare(proj, prep, cos, sin, pairing, rot_dim, ctx.tok_pos, H, d,
                               self.key_scale)
