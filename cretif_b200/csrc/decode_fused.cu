@@ -160,7 +160,7 @@ static int launch_stream(const FusedParams& whole, int tiles, cudaStream_t st) {
   attr[0].val.programmaticStreamSerializationAllowed = g_dependent_launch;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  const int w_rows = EPI == kEpiPlain ? p.N : EPI == kEpiSilu ? 2 * p.I : (p.nh + 2 * p.nkv) * p.hd;
+  const int w_rows = epi_is_plain(EPI) ? p.N : EPI == kEpiSilu ? 2 * p.I : (p.nh + 2 * p.nkv) * p.hd;
   CUtensorMap map_w, map_x;
   if (make_box_map_bf16(&map_w, p.W, w_rows, p.K, p.ldw, 8, kStBoxK, false))
     return dispatch_registers<PRO, EPI>(whole, tiles, st);
@@ -212,9 +212,13 @@ extern "C" int cretif_fused_linear(const void* X, int ldx, const float* H, const
     return kBadArgument;
   const int tiles = (N + kFuRows - 1) / kFuRows;
   cudaStream_t st = (cudaStream_t)stream;
-  if (H) return dispatch_nt<kProNorm, kEpiPlain>(p, tiles, st);
+  const bool ex = p.scaled || p.unary;
+  if (H)
+    return ex ? dispatch_nt<kProNorm, kEpiPlainEx>(p, tiles, st)
+              : dispatch_nt<kProNorm, kEpiPlain>(p, tiles, st);
   if (!X || ldx % 8 || ldx < K || (((uintptr_t)X) & 15)) return kBadArgument;
-  return dispatch_nt<kProPlain, kEpiPlain>(p, tiles, st);
+  return ex ? dispatch_nt<kProPlain, kEpiPlainEx>(p, tiles, st)
+            : dispatch_nt<kProPlain, kEpiPlain>(p, tiles, st);
 }
 
 // q, k, v = norm(h) · Wqkv^T; rotary on q and k; k, v into the cache; q to Q.

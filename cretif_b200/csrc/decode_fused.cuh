@@ -31,7 +31,12 @@ namespace cretif {
 constexpr int kFuWarps = 8;
 constexpr int kFuRows = 16;
 enum Prologue : int { kProPlain = 0, kProNorm = 1 };
-enum Epilogue : int { kEpiPlain = 0, kEpiRope = 1, kEpiSilu = 2 };
+// kEpiPlainEx is kEpiPlain with a factor on the product and an optional activation; it is a
+// kind of its own so that the plain epilogue's code stays what it was.
+enum Epilogue : int { kEpiPlain = 0, kEpiRope = 1, kEpiSilu = 2, kEpiPlainEx = 3 };
+__host__ __device__ constexpr bool epi_is_plain(int epi) {
+  return epi == kEpiPlain || epi == kEpiPlainEx;
+}
 
 // n / d for 0 <= n < 65536 without a division instruction (an integer division in the short
 // dependent chains of these kernels costs about 0.1 us): a shift for powers of two, else a
@@ -119,7 +124,7 @@ __host__ __device__ inline bool derive_fields(FusedParams& p) {
 // Weight row of tile row r (0..15) of CTA `tile`; -1 if beyond the matrix.
 template <int EPI>
 __device__ __forceinline__ int tile_row(const FusedParams& p, int tile, int r) {
-  if (EPI == kEpiPlain) {
+  if (epi_is_plain(EPI)) {
     const int n = tile * kFuRows + r;
     return n < p.N ? n : -1;
   } else if (EPI == kEpiSilu) {
@@ -158,7 +163,7 @@ struct EpiAhead {
 
 template <int NT, int EPI>
 __device__ __forceinline__ void epi_prefetch(const FusedParams& p, int tile, EpiAhead<NT>& a) {
-  if (EPI == kEpiPlain) {
+  if (epi_is_plain(EPI)) {
     if (p.c_dt == kF32 && p.accumulate) {
 #pragma unroll
       for (int it = 0; it < EpiAhead<NT>::kPlainPasses; ++it) {
@@ -196,7 +201,7 @@ template <int NT, int EPI>
 __device__ __forceinline__ void finish_tile(const FusedParams& p, int tile,
                                             float (*red)[kFuRows][8 * NT + 1],
                                             const EpiAhead<NT>& ahead) {
-  if (EPI == kEpiPlain) {
+  if (epi_is_plain(EPI)) {
 #pragma unroll
     for (int it = 0; it < EpiAhead<NT>::kPlainPasses; ++it) {
       const int i = threadIdx.x + it * kFuWarps * 32;
@@ -207,8 +212,10 @@ __device__ __forceinline__ void finish_tile(const FusedParams& p, int tile,
       float sum = 0.f;
 #pragma unroll
       for (int w = 0; w < kFuWarps; ++w) sum += red[w][rr][m];
-      if (p.scaled) sum *= p.alpha;
-      if (p.unary) sum = unary_activation(sum, p.unary - 1);
+      if (EPI == kEpiPlainEx) {
+        if (p.scaled) sum *= p.alpha;
+        if (p.unary) sum = unary_activation(sum, p.unary - 1);
+      }
       if (p.c_dt == kF32) {
         float* out = reinterpret_cast<float*>(p.C) + (size_t)m * p.ldc + n;
         if (p.accumulate) sum += ahead.old[it];
