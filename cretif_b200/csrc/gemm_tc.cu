@@ -76,7 +76,12 @@ struct TcSmem {
 //             matching gate and up columns, and act = silu(gate) * up is stored (BN = 128);
 //   kTcRope   the stacked q|k|v product with one head per tile (BN = head_dim): rotary on q and
 //             k, q to the query buffer, k and v into the block cache at the token's position.
-enum TcEpilogue : int { kTcStore = 0, kTcSilu = 1, kTcRope = 2 };
+enum TcEpilogue : int { kTcStore = 0, kTcSilu = 1, kTcRope = 2, kTcStoreEx = 3 };
+// kTcStoreEx is kTcStore with a factor on the product and an optional activation: a kind of its
+// own, so that the plain store's code and registers stay what they were.
+__host__ __device__ constexpr bool tc_is_store(int epi) {
+  return epi == kTcStore || epi == kTcStoreEx;
+}
 
 struct TcEpi {
   void* C; int ldc, accumulate;                            // store
@@ -127,7 +132,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   unsigned char* smem = reinterpret_cast<unsigned char*>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   using L = TcSmem<BN>;
-  constexpr bool kBulk = EPI == kTcStore && sizeof(TC) == 4;
+  constexpr bool kBulk = tc_is_store(EPI) && sizeof(TC) == 4;
   constexpr bool kBulkSilu = EPI == kTcSilu && EW == 8 && BN == 256;
   constexpr int kSlabs = kBulk ? EW / 2 : (kBulkSilu ? 2 : 0);     // two a group of four warps
   unsigned char* staging = smem + kTcStages * L::kStage;
@@ -302,7 +307,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       // tokens: o-proj 40 -> 52 us; K = 8192: 76 -> 84 us).
       constexpr int kCols = BN / halves;                 // this thread's columns of the tile
       const int c_first = chalf * kCols;
-      const bool pre = EPI == kTcStore && sizeof(TC) == 4 && EW == 4 && accumulate && num_kb <= 24;
+      const bool pre = tc_is_store(EPI) && sizeof(TC) == 4 && EW == 4 && accumulate && num_kb <= 24;
       float4 oldv[8];
       auto fetch_old = [&](int c0) {
 #pragma unroll
@@ -340,7 +345,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           if (elected) tc::bulk_wait_group_read<1>();       // the slab used two slabs ago is free
           asm volatile("bar.sync %0, 128;" ::"r"(1 + chalf) : "memory");
           unsigned char* slab = mine + (slabs & 1) * L::kSlab;
-          if (ep.scaled) {
+          if (EPI == kTcStoreEx && ep.scaled) {
 #pragma unroll
             for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(ep.alpha * __uint_as_float(r[j]));
           }
@@ -355,7 +360,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             tc::bulk_commit_group();
           }
         }
-      } else if (ok && EPI == kTcStore) {
+      } else if (ok && tc_is_store(EPI)) {
 #pragma unroll 1
         for (int c0 = c_first; c0 < c_first + kCols; c0 += 32) {
           uint32_t r[32];
@@ -374,11 +379,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
               float v[8];
 #pragma unroll
               for (int e = 0; e < 8; ++e) v[e] = __uint_as_float(r[j + e]);
-              if (ep.scaled) {
+              if (EPI == kTcStoreEx && ep.scaled) {
 #pragma unroll
                 for (int e = 0; e < 8; ++e) v[e] *= ep.alpha;
               }
-              if (ep.unary) {
+              if (EPI == kTcStoreEx && ep.unary) {
 #pragma unroll
                 for (int e = 0; e < 8; ++e) v[e] = unary_activation(v[e], ep.unary - 1);
               }
@@ -633,7 +638,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   unsigned char* smem = reinterpret_cast<unsigned char*>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   using L = TpSmem<kTpBN>;
-  constexpr int kSlabs = EPI == kTcStore ? 4 : 2;
+  constexpr int kSlabs = tc_is_store(EPI) ? 4 : 2;
   unsigned char* staging = smem + n_stages * L::kStage;
   uint64_t* full = reinterpret_cast<uint64_t*>(staging + kSlabs * L::kSlab);   // used in CTA 0
   uint64_t* empty = full + kTcMaxStages;
@@ -739,7 +744,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       const bool ok = alive;
       tc::tc_fence_after();
       const uint32_t lane_acc = tmem_acc + (uint32_t)(buf * kTpBN) + ((uint32_t)(quad * 32) << 16);
-      if (EPI == kTcStore) {
+      if (tc_is_store(EPI)) {
         unsigned char* mine = staging + chalf * 2 * L::kSlab;
         const bool elected = ((warp - 2) & 3) == 0 && lane == 0;
 #pragma unroll 1
@@ -750,7 +755,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
           if (elected) tc::bulk_wait_group_read<1>();
           asm volatile("bar.sync %0, 128;" ::"r"(1 + chalf) : "memory");
           unsigned char* slab = mine + (slabs & 1) * L::kSlab;
-          if (ep.scaled) {
+          if (EPI == kTcStoreEx && ep.scaled) {
 #pragma unroll
             for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(ep.alpha * __uint_as_float(r[j]));
           }
@@ -808,7 +813,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       __syncwarp();
       if (lane == 0) tc::mbar_arrive_cluster(acc_empty_leader[buf]);
     }
-    if (((EPI == kTcStore && ((warp - 2) & 3) == 0) || (EPI != kTcStore && warp == 2)) && lane == 0)
+    if (((tc_is_store(EPI) && ((warp - 2) & 3) == 0) || (!tc_is_store(EPI) && warp == 2)) && lane == 0)
       tc::bulk_wait_all();
   }
   if (*abort && threadIdx.x == 0) atomicOr(fault, kFaultWaitExpired);
@@ -928,7 +933,7 @@ static int launch_tc_pair(const void* A, const void* W, TcEpi ep, int M, int N, 
   CUtensorMap map_a, map_w, map_c;
   if (make_tile_map_bf16(&map_a, A, M, K, lda, kTcBM)) return kBadArgument;
   if (make_tile_map_bf16(&map_w, W, N, K, ldw, kTpBN / 2)) return kBadArgument;
-  if (EPI == kTcStore ? make_box_map(&map_c, ep.C, M, N, ep.ldc, kTcBM, 32, true, true)
+  if (tc_is_store(EPI) ? make_box_map(&map_c, ep.C, M, N, ep.ldc, kTcBM, 32, true, true)
                       : make_box_map(&map_c, ep.act, M, ep.I, ep.I, kTcBM, 64, true, false))
     return kBadArgument;
   static int sm_count = 0;
@@ -941,7 +946,7 @@ static int launch_tc_pair(const void* A, const void* W, TcEpi ep, int M, int N, 
   const int n_n_tiles = (N + kTpBN - 1) / kTpBN;
   const long long tiles = (long long)n_n_tiles * ((M + 2 * kTcBM - 1) / (2 * kTcBM));
   if (tiles > 0x7fffffffLL) return kBadArgument;
-  constexpr int kSlabs = EPI == kTcStore ? 4 : 2;
+  constexpr int kSlabs = tc_is_store(EPI) ? 4 : 2;
   int stages = kTcMaxStages;
   while (stages > 2 && TpSmem<kTpBN>::total(stages, kSlabs) > 227 * 1024) --stages;
   const int smem = TpSmem<kTpBN>::total(stages, kSlabs);
@@ -1053,7 +1058,7 @@ static int launch_tc(const void* A, const void* W, const TcEpi& ep_in, int M, in
   // 2,048 x 2,048 x 2,048 28.2 -> 26.1; with K = 8,192 the stages it takes away cost more than
   // it saves (69.6 -> 94.2).
   ep.bulk = 0;
-  if (EPI == kTcStore && sizeof(TC) == 4 && ep.accumulate && K <= 4096 && g_tc_bulk_add && ep.ldc % 4 == 0 && ((uintptr_t)ep.C & 15) == 0 &&
+  if (tc_is_store(EPI) && sizeof(TC) == 4 && ep.accumulate && K <= 4096 && g_tc_bulk_add && ep.ldc % 4 == 0 && ((uintptr_t)ep.C & 15) == 0 &&
       make_box_map(&map_c, ep.C, M, N, ep.ldc, kTcBM, 32, true, true) == 0) {
     ep.bulk = 1;
     stages = TcSmem<BN>::stages_with_staging(stages, epi_warps / 2);
@@ -1151,13 +1156,17 @@ extern "C" int cretif_gemm_tc(const void* A, const void* W, void* C, int c_dt, i
   if (c_dt == kF32 && accumulate && g_tc_pair != 0 && g_tc_bulk_add && (bn == 256 || bn == 192) &&
       N % bn == 0 && ldc % 4 == 0 &&
       (g_tc_pair > 0 || ((long long)((M + 255) / 256) * (N / bn) >= 2 * 74 && pair_pays(N, K)))) {
+    if (ep.scaled)
+      return bn == 256 ? launch_tc_pair<256, kTcStoreEx>(A, W, ep, M, N, K, lda, ldw, fault, st)
+                       : launch_tc_pair<192, kTcStoreEx>(A, W, ep, M, N, K, lda, ldw, fault, st);
     return bn == 256 ? launch_tc_pair<256, kTcStore>(A, W, ep, M, N, K, lda, ldw, fault, st)
                      : launch_tc_pair<192, kTcStore>(A, W, ep, M, N, K, lda, ldw, fault, st);
   }
-#define CRETIF_TC(BN)                                                                         \
-  (c_dt == kBF16 ? launch_tc<BN, kTcStore, __nv_bfloat16>(A, W, ep, M, N, K, lda, ldw, fault, \
-                                                          st)                                 \
-                 : launch_tc<BN, kTcStore, float>(A, W, ep, M, N, K, lda, ldw, fault, st))
+#define CRETIF_TC_AS(BN, EPI)                                                                  \
+  (c_dt == kBF16 ? launch_tc<BN, EPI, __nv_bfloat16>(A, W, ep, M, N, K, lda, ldw, fault, st)   \
+                 : launch_tc<BN, EPI, float>(A, W, ep, M, N, K, lda, ldw, fault, st))
+#define CRETIF_TC(BN) \
+  ((ep.scaled || ep.unary) ? CRETIF_TC_AS(BN, kTcStoreEx) : CRETIF_TC_AS(BN, kTcStore))
   if (c_dt != kBF16 && c_dt != kF32) return kBadDType;
   if (c_dt == kBF16 && accumulate) return kBadArgument;
   switch (bn) {
@@ -1168,6 +1177,7 @@ extern "C" int cretif_gemm_tc(const void* A, const void* W, void* C, int c_dt, i
     default: return kBadArgument;
   }
 #undef CRETIF_TC
+#undef CRETIF_TC_AS
 }
 
 // act[M, I] = silu(A·Wg^T) * (A·Wu^T); Wgu holds gate and up rows interleaved in blocks of 64.

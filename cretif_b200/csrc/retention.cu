@@ -39,7 +39,9 @@ retention_prepare_kernel(const float* __restrict__ proj, int ldp, float* __restr
   const float* row = proj + (size_t)t * ldp;
   float* out = prep + (size_t)t * ldo;
   const int n = 2 * H * d;
-  for (int idx = threadIdx.x; idx < n; idx += blockDim.x) {
+  // (a step of few tokens spreads a token's columns over blockIdx.y: one round trip to memory
+  // a thread instead of a chain of them)
+  for (int idx = blockIdx.y * blockDim.x + threadIdx.x; idx < n; idx += blockDim.x * gridDim.y) {
     const int head = idx / d, i = idx - head * d;
     float v = row[idx];
     if (i < rot_dim) {
@@ -401,6 +403,7 @@ retention_carry_kernel(const float* __restrict__ prep, int ldp, const float* __r
     ret_cp_commit();
   };
   stage(t0, smem);
+  __syncthreads();                         // the table of powers is read before the loop's barrier
   int turn = 0;
   for (int c0 = t0; c0 < t1; c0 += C, ++turn) {
     const int nt = min(C, t1 - c0);
@@ -556,7 +559,9 @@ extern "C" int cretif_retention_prepare(const float* proj, int ldp, float* prep,
       ldo < 2 * H * d)
     return kBadArgument;
   if (rot_dim > 0 && (!cos_t || !sin_t)) return kBadArgument;
-  retention_prepare_kernel<<<T, 256, 0, (cudaStream_t)stream>>>(
+  const int per_token = T < 64 ? (2 * H * d + 255) / 256 : 1;
+  retention_prepare_kernel<<<dim3(T, per_token > 65535 ? 65535 : per_token), 256, 0,
+                             (cudaStream_t)stream>>>(
       proj, ldp, prep, ldo, cos_t, sin_t, pairing, rot_dim, tok_pos, H, d, k_scale);
   return launch_status();
 }

@@ -212,3 +212,23 @@ def test_a_further_pass_gets_the_input_again():
     x1 = layer(x0)
     assert torch.allclose(streams[0], x1)
     assert torch.allclose(streams[1], layer(x1 + x0))
+
+
+def test_the_bench_configurations_build():
+    """The models `bench.py --design virorax` measures parse and give a schedule with as many
+    layer runs as the models beside them have layers."""
+    import importlib.util
+    import os
+    path = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "bench.py")
+    mod_spec = importlib.util.spec_from_file_location("bench_for_test", path)
+    bench = importlib.util.module_from_spec(mod_spec)
+    mod_spec.loader.exec_module(bench)
+    for size, z in bench.DESIGN_SIZES.items():
+        for layers in (4, 8):
+            for name, cfg in bench.virorax_configs(z, layers).items():
+                if not name.startswith("virorax"):
+                    continue
+                spec = _spec(cfg)
+                spec.validate()
+                assert len(spec.schedule) == layers, (size, name)
+                assert spec.architecture == "Virorax"
