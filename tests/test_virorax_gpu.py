@@ -734,3 +734,26 @@ def test_the_replay_program_runs_a_virorax_folder(folders, tmp_path):
     got1 = np.fromfile(out / "1.f32", dtype="<f4").reshape(1, -1)
     assert not (out / "2.f32").exists()
     assert rel_err(got0, want[[0, 19, 6]]) <= 1e-4 and rel_err(got1, want[[20]]) <= 1e-4
+
+
+def test_the_command_line_writes_and_runs_a_virorax_folder(tmp_path):
+    """``python -m cretif_b200``: a folder with random weights from a config.json, then greedy
+    generation from token ids, the same tokens as the entry point gives."""
+    import subprocess
+    import sys
+    import cretif_b200
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cfg_file = tmp_path / "cfg.json"
+    cfg_file.write_text(json.dumps(tiny.V_A))
+    folder = str(tmp_path / "model")
+    env = dict(os.environ, PYTHONPATH=root)
+    r = subprocess.run([sys.executable, "-m", "cretif_b200", folder, "5,6,7,8", "6", "--dtype",
+                        "float32", "--random-weights", "21", "--config", str(cfg_file)],
+                       capture_output=True, text=True, timeout=600, env=env, cwd=root)
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert "model: Virorax" in r.stdout
+    line = [l for l in r.stdout.splitlines() if l.startswith("generated ids:")][0]
+    got = json.loads(line[len("generated ids:"):line.index("(")].strip())
+    eng = cretif_b200.load(folder, dtype="float32", max_tokens=512)
+    want = eng.generate([[5, 6, 7, 8]], max_tokens=6, stop_ids=[])[0].tokens
+    assert got == want and len(got) == 6
