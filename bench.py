@@ -370,18 +370,18 @@ def virorax_configs(z, layers):
     of each head, the retention heads decay over 32 to 2,048 tokens."""
     att = {"heads": z["heads"], "kv_heads": z["kv"], "dim": z["dim"], "vdim": z["dim"],
            "scale": z["dim"] ** -0.5, "mask": {"size": z["window"]},
-           "rot": {"base": 250000.0, "dims": z["dim"] // 2}}
+           "rot": {"base": 10000.0, "dims": z["dim"] // 2}}
     H = z["d_heads"]
     ret = {"heads": H, "dim": z["d_dim"], "vdim": z["d_vdim"],
            "decay": [1.0 - 2.0 ** (-5.0 - 6.0 * h / max(1, H - 1)) for h in range(H)],
-           "rot": {"base": 1000000.0, "dims": z["d_dim"]}}
+           "rot": {"base": 500000.0, "dims": z["d_dim"]}}
     mlp = {"kind": "dense", "ff": z["ff"]}
     kinds = {"attention": att, "retention": ret}
 
     def virorax(order, loop=None):
         cfg = {"architecture": "Virorax", "vocab": z["vocab"], "width": z["width"],
-               "norm": {"eps": 1e-6}, "max_positions": CONTEXT, "residual_mult": 0.7,
-               "logit_softcap": 15.0,
+               "norm": {"eps": 1e-6}, "max_positions": CONTEXT, "residual_mult": 0.6,
+               "logit_softcap": 30.0,
                "layers": [{"type": k, "mixer": kinds[k], "mlp": mlp} for k in order]}
         if loop:
             cfg["loop"] = loop
