@@ -2,13 +2,13 @@
 //
 // Per token and head, with state S [d, e] (32-bit, zero at a sequence's start):
 //     S <- decay_h S + k v^T;   o = S^T q
-// so the read-out sees the token's own write.  Three kernels serve any step shape (whole
-// prompts, further chunks at a cached position, single tokens), all arithmetic in 32-bit;
-// the recurrence has a token-by-token form and a form of 64 tokens at a time (further down):
+// so the read-out sees the token's own write.  Any step shape is served (whole prompts, further
+// chunks at a cached position, single tokens), all arithmetic in 32-bit; the recurrence has a
+// token-by-token form and a form of 64 tokens at a time (further down):
 //
-// * retention_prepare (a CTA per token): the first rot_dim channels of every query and key head
-//   are rotated by the token's position (cos/sin from a 32-bit table), the key is multiplied
-//   by k_scale after the rotation.
+// * retention_prepare (a CTA per token, or several where a step has few tokens): the first
+//   rot_dim channels of every query and key head are rotated by the token's position (cos/sin
+//   from a 32-bit table), the key is multiplied by k_scale after the rotation.
 // * retention_recurrence (a CTA per (sequence, head, slice of columns)): the columns of S are
 //   independent; a group of P lanes owns one column, each lane R contiguous rows of it in
 //   registers.  Tokens go in chunks of 16 whose q, k and v are staged in shared memory (a

@@ -107,15 +107,14 @@ class Retention(Part):
             pairing = rot_dim = 0
         else:
             raise ValueError("retention takes a rotary position encoding or none")
-        x = proj
-        prep = torch.empty((T, 2 * H * d), dtype=torch.float32, device=x.device)
+        prep = torch.empty((T, 2 * H * d), dtype=torch.float32, device=proj.device)
         ops.retention_prepare(proj, prep, cos, sin, pairing, rot_dim, ctx.tok_pos, H, d,
                               self.key_scale)
-        o_raw = torch.empty((T, H * e), dtype=torch.float32, device=x.device)
+        o_raw = torch.empty((T, H * e), dtype=torch.float32, device=proj.device)
         ops.retention_recurrence(prep, proj[:, 2 * H * d:2 * H * d + H * e], self.decay,
                                  cache.state, ctx.cu_seqlens, ctx.seq_slot, ctx.B, H, d, e,
                                  o_raw, write_state=cache.writes)
-        out = torch.empty((T, H * e), dtype=self.dtype, device=x.device)
+        out = torch.empty((T, H * e), dtype=self.dtype, device=proj.device)
         ops.heads_out_norm(o_raw, proj[:, 2 * H * d + H * e:2 * H * d + 2 * H * e], None,
                            self.eps, out, H, e)
         if into is not None:
