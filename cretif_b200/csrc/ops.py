@@ -476,8 +476,8 @@ def retention_recurrence(prep, v, decay, state, cu_seqlens, seq_slot, B: int, H:
     """``S <- decay_h S + k vᵀ; o = Sᵀ q`` over the step's tokens of every (sequence, head), from
     and to ``state`` (view [slots, H·d·e] float32); ``prep`` [T, 2Hd] holds q and k, ``v``
     [T, >= He] the values (float32), ``o_raw`` [T, He] receives the read-outs.  ``form``:
-    ``"token"`` walks the tokens one by one, ``"chunk"`` takes 64 at a time as three matrix
-    products (refused where sizes or addresses rule out 16-byte accesses), ``"auto"`` takes
+    ``"token"`` walks the tokens one by one, ``"chunk"`` takes 64 at a time as matrix products
+    in two kernels (refused where sizes or addresses rule out 16-byte accesses), ``"auto"`` takes
     chunks where the step brings 16 tokens a sequence or more and they are allowed."""
     _need(prep, "prep", torch.float32, 2); _need(v, "v", torch.float32, 2)
     _need(decay, "decay", torch.float32, 1); _need(state, "state", torch.float32, 2)
