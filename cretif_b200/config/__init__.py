@@ -6,6 +6,7 @@ from .llama import LlamaConfig, build_llama_spec, llama_config_from_dict
 from .rigozen import RigozenConfig, build_rigozen_spec, rigozen_config_from_dict
 from .losorax import LosoraxConfig, build_losorax_spec, losorax_config_from_dict
 from .virorax import ViroraxConfig, build_virorax_spec, virorax_config_from_dict
+from .mipurax import MipuraxConfig, build_mipurax_spec, mipurax_config_from_dict
 from .presets import PRESETS, preset
 
 __all__ = [
@@ -16,4 +17,5 @@ __all__ = [
     "RigozenConfig", "build_rigozen_spec", "rigozen_config_from_dict",
     "LosoraxConfig", "build_losorax_spec", "losorax_config_from_dict",
     "ViroraxConfig", "build_virorax_spec", "virorax_config_from_dict",
+    "MipuraxConfig", "build_mipurax_spec", "mipurax_config_from_dict",
 ]

@@ -118,11 +118,34 @@ int cretif_general_delta_recurrence(const float* proj, int ldp, const float* pre
                                     float eps, float* o_raw, void* out, int out_dt, int ldo,
                                     int write_state, int T, void* stream);
 
+// Attention over a cached latent (latent_ops.cu).  A projection row holds
+// [cq (q_rank) | c (rank) | kr (rot) | ...]: cq and c are brought to unit RMS and multiplied by wq
+// and wc, kr is rotated by the token's position; cq goes to cq_out, [c | kr] into the token's row
+// of the key cache (one key/value head of size rank + rot).  pairing 0: channel i with
+// i + rot/2, 1: channel 2i with 2i + 1.
+int cretif_latent_in(const void* proj, int ldp, int proj_dt, int q_rank, int rank, int rot,
+                     const float* wq, const float* wc, float eps, const float* cos_t,
+                     const float* sin_t, int pairing, const int* tok_pos, const int* tok_seq,
+                     const int* seq_slot, void* cq_out, int ldq, int dt, const int* table,
+                     int table_stride, void* kc, int bt, int write_cache, int T,
+                     unsigned int* fault, void* stream);
+// q [T, nh (d + rot)]: the last rot channels of every head, rotated, go to
+// out[t, h * ldh + off ...].
+int cretif_rope_heads(const void* q, int ldq, int q_dt, int nh, int d, int rot, const float* cos_t,
+                      const float* sin_t, int pairing, const int* tok_pos, void* out, int ldo,
+                      int ldh, int off, int dt, int T, void* stream);
+// x <- x / sqrt(mean(x^2) + eps) * w in place, float32 rows.
+int cretif_rmsnorm_rows(float* x, int ld, const float* w, int R, int H, float eps, void* stream);
+
 // Routed experts (moe.cu).
+// groups > 1: the experts form that many equal groups of neighbours, a group's score is the sum
+// of its two largest logistic scores, only experts of the `keep` best groups can be chosen.
+// renorm: the chosen scores are divided by (their sum + sum_eps).
 int cretif_moe_route(const void* x, int x_dt, int ldx, const float* router_w, int E, int H,
-                     int top, int renorm, int* ids, float* wts, int T, void* stream);
-int cretif_moe_topk(const float* logits, int ld, int E, int top, int renorm, int* ids, float* wts,
-                    int T, void* stream);
+                     int top, int renorm, int groups, int keep, float sum_eps, int* ids,
+                     float* wts, int T, void* stream);
+int cretif_moe_topk(const float* logits, int ld, int E, int top, int renorm, int groups, int keep,
+                    float sum_eps, int* ids, float* wts, int T, void* stream);
 int cretif_moe_group(const int* ids, int P, int E, int* offsets, int* place, int* order,
                      int* tile_expert, int* tile_row0, int max_tiles, void* stream);
 int cretif_moe_gemm(const void* A, int a_dt, int lda, const void* W, int w_dt, void* C, int ldc,
@@ -169,7 +192,8 @@ int cretif_gemm_skinny_max_rows(void);
 // C[M,N] (= or +=) A[M,K] · W[N,K]^T on the tcgen05 tensor cores (TMA + TMEM), bfloat16
 // operands, C bfloat16 or float32 (+= only float32).  bn = 64/128/192/256 picks the tile width,
 // 0 lets the launcher choose.  The product is multiplied by alpha before it is stored or added;
-// unary (0 none, 1 relu^2, 2 gelu in its tanh form, 3 silu; stores only) is applied to the
+// unary (0 none, 1 relu^2, 2 gelu in its tanh form, 3 silu, 4 gelu with the error function;
+// stores only) is applied to the
 // 32-bit sums before they are rounded.  A wait that expires sets bit 2 of *fault.
 int cretif_gemm_tc(const void* A, const void* W, void* C, int c_dt, int M, int N, int K, int lda,
                    int ldw, int ldc, int accumulate, int bn, float alpha, int unary,
@@ -199,6 +223,11 @@ int cretif_gemm_tc_silu(const void* A, const void* Wgu, void* act, int M, int I,
 int cretif_gemm_tc_grouped(const void* A, const void* W, void* C, int M, int N, int K, int lda,
                            int ldw, int ldc, int groups, const int* tile_group,
                            const int* used_m_tiles, unsigned int* fault, void* stream);
+// C bfloat16 [M, N] = act(A W[g]^T): unary = 1 + a kind of cretif_activation.
+int cretif_gemm_tc_act_grouped(const void* A, const void* W, void* C, int M, int N, int K, int lda,
+                               int ldw, int ldc, int groups, const int* tile_group,
+                               const int* used_m_tiles, int unary, unsigned int* fault,
+                               void* stream);
 int cretif_gemm_tc_silu_grouped(const void* A, const void* Wgu, void* act, int M, int I, int K,
                                 int lda, int ldw, int groups, const int* tile_group,
                                 const int* used_m_tiles, unsigned int* fault, void* stream);
@@ -214,11 +243,14 @@ int cretif_gemm_tc_qkv_rope(const void* A, const void* Wqkv, void* Q, int ldq, c
 // vd: size of a value head (the cache's values are [blocks, nkv, bt, vd], out rows nh * vd).
 // bias (may be null): float32 [bias_rows, nh] added to the scaled score of the key n positions
 // back, row = the last r with bias_edges[r] <= n (edges ascending, edges[0] = 0).
+// slope (may be null): float32 [nh]; slope[h] * n is taken off that score.
+// window, here and in every attention entry point: > 0 a sliding window of that many keys,
+// < 0 chunks of -window positions counted from 0 (a query sees the keys of its own chunk), 0 all.
 int cretif_attn_simt(const void* q, int ldq, void* out, int ldo, int dt, const void* kc,
                      const void* vc, const int* table, int table_stride, const int* tok_pos,
                      const int* tok_seq, const int* seq_slot, int nh, int nkv, int hd, float scale,
                      int window, int bt, int T, const float* sink, int vd, const float* bias,
-                     const int* bias_edges, int bias_rows, void* stream);
+                     const int* bias_edges, int bias_rows, const float* slope, void* stream);
 
 // Decode attention (one query token per sequence), bfloat16, keys split into n_splits <= 64
 // ranges per (sequence, kv head); part_o/part_ml are float32 scratch of the sizes that
@@ -338,7 +370,8 @@ int cretif_headnorm_rope_kv_append(const void* proj, int ldp, int proj_dt, const
 // o[t, h, :] *= sigmoid(g[t, h]) for nh heads of vd channels.
 int cretif_gate_heads(void* o, int ldo, int dt, const float* g, int ldg, int nh, int vd, int T,
                       void* stream);
-// out = act(in) element by element: kind 0 relu(z)^2, 1 gelu in its tanh form, 2 silu.
+// out = act(in) element by element: kind 0 relu(z)^2, 1 gelu in its tanh form, 2 silu,
+// 3 gelu with the error function.
 int cretif_activation(const void* in, int ldi, int in_dt, void* out, int ldo, int out_dt, int T,
                       int width, int kind, void* stream);
 // z <- cap * tanh(z / cap) in place.

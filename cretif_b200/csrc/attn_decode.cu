@@ -83,7 +83,7 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int ldq,
   const int pos = tok_pos[b];
   const int slot = seq_slot[tok_seq[b]];
   const int* tab = table + (size_t)slot * table_stride;
-  const int first_key = window > 0 ? max(0, pos - window + 1) : 0;
+  const int first_key = first_visible_key(pos, window);
   const int first_tile = first_key / kDecTile, n_tiles = pos / kDecTile + 1;
   const int per = (n_tiles - first_tile + n_splits - 1) / n_splits;
   const int t_begin = first_tile + split * per, t_end = min(n_tiles, t_begin + per);
@@ -357,7 +357,7 @@ extern "C" int cretif_attn_decode(const void* q, int ldq, void* out, int ldo, co
   if (B <= 0) return kOk;
   if (nh <= 0 || nkv <= 0 || nh % nkv || nh / nkv > kDecMaxGroup || hd % 16 || hd < 16 ||
       hd > 256 || bt != kDecTile || n_splits <= 0 || n_splits > kDecTile || nkv > 65535 ||
-      B > 65535 || window < 0)
+      B > 65535)
     return kBadArgument;
   if (((uintptr_t)kc | (uintptr_t)vc) & 15) return kMisaligned;
   cudaStream_t st = (cudaStream_t)stream;

@@ -126,7 +126,7 @@ extern "C" int cretif_attn_decode_mma_bias(const void* q, int ldq, void* out, in
   const DistanceBias bias{bias_near, bias_far, n_far};
   if (nh <= 0 || nkv <= 0 || nh % nkv || nh / nkv > 8 || hd % 16 || hd < 16 || hd > 128 ||
       bt != kDmTile || n_splits <= 0 || n_splits > kDmTile || nkv > 65535 || B > 65535 ||
-      window < 0 || ldq % 2)
+      ldq % 2)
     return kBadArgument;
   if (((uintptr_t)kc | (uintptr_t)vc) & 15 || ((uintptr_t)q & 3)) return kMisaligned;
   const long long cache_rows = n_blocks * nkv * kDmTile;

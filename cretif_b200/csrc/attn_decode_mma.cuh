@@ -156,7 +156,7 @@ __device__ __forceinline__ void attn_decode_mma_item(
   const int pos = tok_pos[b];
   const int slot = seq_slot[tok_seq[b]];
   const int* tab = table + (size_t)slot * table_stride;
-  const int first_key = window > 0 ? max(0, pos - window + 1) : 0;
+  const int first_key = first_visible_key(pos, window);
   const int first_tile = first_key / kDmTile, n_tiles = pos / kDmTile + 1;
   // the tiles are dealt out evenly: the first (tiles % ranges) ranges take one more
   const int span = n_tiles - first_tile, per = span / n_splits, extra = span - per * n_splits;

@@ -145,7 +145,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
   const int* tab = table + (size_t)slot * table_stride;
   const int rows_here = min(kPfBQ, n_new - q0);
   const int pos_first = start + q0, pos_last = start + q0 + rows_here - 1;
-  const int key_lo = window > 0 ? max(0, pos_first - window + 1) : 0;
+  const int key_lo = first_visible_key(pos_first, window);
   const int blk_lo = key_lo / kPfBlk, blk_hi = pos_last / kPfBlk;      // cache blocks, inclusive
   const int n_tiles = (blk_hi - blk_lo + 2) / 2;                        // steps of two blocks
   // Tensor memory: two score tiles (the product of step j + 1 runs under the softmax of
@@ -261,10 +261,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
     const int row = quad * 32 + lane;
     const int q_pos = start + q0 + row;
     const bool row_valid = row < rows_here;
-    const int lo_key = window > 0 ? max(0, q_pos - window + 1) : 0;
+    const int lo_key = first_visible_key(q_pos, window);
     // a step needs masks if it reaches past the first row's position or starts before the
     // last row's window
-    const int lo_key_last = window > 0 ? max(0, start + q0 + kPfBQ - 1 - window + 1) : 0;
+    const int lo_key_last = first_visible_key(start + q0 + kPfBQ - 1, window);
     const uint32_t lane_addr = tmem + ((uint32_t)(quad * 32) << 16);
     const int ocols = hd >> 1, obase = half * ocols;     // this thread's output columns
     float o[HDMAX / 2];
@@ -945,7 +945,7 @@ extern "C" int cretif_attn_prefill_tc_bias(const void* qkv, int ldq, int T, void
   if ((bias_near != nullptr) != (bias_far != nullptr) || (bias_near && (n_far < 1 || n_far > 8192)))
     return kBadArgument;
   if (nh <= 0 || nkv <= 0 || nh % nkv || hd % 16 || hd < 16 || hd > 128 || bt != kPfBlk ||
-      window < 0 || !(scale > 0.f) || max_new <= 0 || B > 65535 || ldq % 8 || ldo % 8 ||
+      !(scale > 0.f) || max_new <= 0 || B > 65535 || ldq % 8 || ldo % 8 ||
       (max_new + kPfBQ - 1) / kPfBQ > 65535)
     return kBadArgument;
   if (((uintptr_t)qkv | (uintptr_t)kc | (uintptr_t)vc | (uintptr_t)out) & 15) return kMisaligned;

@@ -20,6 +20,10 @@
 // n = pos - key positions back adds bias[r, h] to its scaled score, where r is the last row
 // with edges[r] <= n.  The host lays the edges out (a row per distance, then rows spaced by the
 // logarithm, or anything else that is monotone); the kernel only searches them.
+//
+// Slope by distance: slope[heads]; a key n positions back has slope[h] * n taken off its scaled
+// score.  The mask is first_visible_key(pos, window): every key, a sliding window, or the
+// query's own chunk of positions.
 #include "api.h"
 #include "common.cuh"
 
@@ -38,7 +42,7 @@ attn_simt_kernel(const T* __restrict__ q, int ldq, T* __restrict__ out, int ldo,
                  const int* __restrict__ seq_slot, int nh, int nkv, int hd, float scale,
                  int window, int bt, int T_tokens, const float* __restrict__ sink, int vd,
                  const float* __restrict__ bias, const int* __restrict__ bias_edges,
-                 int bias_rows) {
+                 int bias_rows, const float* __restrict__ slope) {
   __shared__ float qs[kMaxHd];
   __shared__ float bias_s[kMaxBiasRows];
   __shared__ int edge_s[kMaxBiasRows];
@@ -51,7 +55,8 @@ attn_simt_kernel(const T* __restrict__ q, int ldq, T* __restrict__ out, int ldo,
   const int pos = tok_pos[t];
   const int slot = seq_slot[tok_seq[t]];
   const int* tab = table + (size_t)slot * table_stride;
-  const int first = window > 0 ? max(0, pos - window + 1) : 0;
+  const int first = first_visible_key(pos, window);
+  const float tilt = slope ? slope[h] : 0.f;
 
   const T* qrow = q + (size_t)t * ldq + (size_t)h * hd;
   for (int d = threadIdx.x; d < hd; d += kWarps * 32) qs[d] = to_float(qrow[d]);
@@ -90,6 +95,7 @@ attn_simt_kernel(const T* __restrict__ q, int ldq, T* __restrict__ out, int ldo,
         for (int d = 0; d < hd; ++d) dot = fmaf(qs[d], to_float(kp[d]), dot);
       }
       s = dot * scale;
+      if (slope) s -= tilt * (float)(pos - key);
       if (bias) {
         // the last row whose edge is at or below the distance
         const int n = pos - key;
@@ -195,10 +201,11 @@ extern "C" int cretif_attn_simt(const void* q, int ldq, void* out, int ldo, int 
                                 const int* tok_pos, const int* tok_seq, const int* seq_slot,
                                 int nh, int nkv, int hd, float scale, int window, int bt, int T,
                                 const float* sink, int vd, const float* bias,
-                                const int* bias_edges, int bias_rows, void* stream) {
+                                const int* bias_edges, int bias_rows, const float* slope,
+                                void* stream) {
   if (T <= 0) return kOk;
   if (nh <= 0 || nkv <= 0 || nh % nkv || hd <= 0 || hd > kMaxHd || bt <= 0 ||
-      window < 0 || vd <= 0 || vd > kMaxHd)
+      vd <= 0 || vd > kMaxHd)
     return kBadArgument;
   if (bias && (!bias_edges || bias_rows <= 0 || bias_rows > kMaxBiasRows)) return kBadArgument;
   cudaStream_t st = (cudaStream_t)stream;
@@ -209,12 +216,12 @@ extern "C" int cretif_attn_simt(const void* q, int ldq, void* out, int ldo, int 
     attn_simt_kernel<float><<<blocks, kWarps * 32, 0, st>>>(
         (const float*)q, ldq, (float*)out, ldo, (const float*)kc, (const float*)vc, table,
         table_stride, tok_pos, tok_seq, seq_slot, nh, nkv, hd, scale, window, bt, T, sink, vd, bias,
-        bias_edges, bias_rows);
+        bias_edges, bias_rows, slope);
   else if (dt == kBF16)
     attn_simt_kernel<__nv_bfloat16><<<blocks, kWarps * 32, 0, st>>>(
         (const __nv_bfloat16*)q, ldq, (__nv_bfloat16*)out, ldo, (const __nv_bfloat16*)kc,
         (const __nv_bfloat16*)vc, table, table_stride, tok_pos, tok_seq, seq_slot, nh, nkv, hd,
-        scale, window, bt, T, sink, vd, bias, bias_edges, bias_rows);
+        scale, window, bt, T, sink, vd, bias, bias_edges, bias_rows, slope);
   else
     return kBadDType;
   return launch_status();

@@ -159,7 +159,9 @@ void count_variant(int v);
 // before them (decode_fused.cu owns the switch).
 int dependent_launch_enabled();
 
-// Activations of a feed-forward without a gate: 0 relu(z)^2, 1 gelu (tanh form), 2 silu.
+// Activations of a feed-forward without a gate: 0 relu(z)^2, 1 gelu (tanh form), 2 silu,
+// 3 gelu (the exact form, with the error function).
+constexpr int kUnaryKinds = 4;
 __device__ __forceinline__ float unary_activation(float z, int kind) {
   if (kind == 0) {
     const float r = fmaxf(z, 0.f);
@@ -167,7 +169,17 @@ __device__ __forceinline__ float unary_activation(float z, int kind) {
   }
   if (kind == 1)
     return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+  if (kind == 3) return 0.5f * z * (1.0f + erff(z * 0.7071067811865476f));
   return z / (1.0f + expf(-z));
+}
+
+// The first key a query at position pos sees.  window > 0: a sliding window of that many keys
+// (the query's own included); window < 0: chunks of -window positions counted from position 0 of
+// the sequence, a query sees the keys of its own chunk; 0: every key.  It never decreases with pos.
+__host__ __device__ __forceinline__ int first_visible_key(int pos, int window) {
+  if (window > 0) return pos - window + 1 > 0 ? pos - window + 1 : 0;
+  if (window < 0) return pos - pos % (-window);
+  return 0;
 }
 
 inline int launch_status() {

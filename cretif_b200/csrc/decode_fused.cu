@@ -201,7 +201,7 @@ extern "C" int cretif_fused_linear(const void* X, int ldx, const float* H, const
                                    int c_dt, int ldc, int accumulate, float alpha, int unary,
                                    int M, int N, int K, unsigned int* fault, void* stream) {
   if (M <= 0 || N <= 0) return kOk;
-  if (unary < 0 || unary > 3 || (unary && accumulate)) return kBadArgument;
+  if (unary < 0 || unary > kUnaryKinds || (unary && accumulate)) return kBadArgument;
   FusedParams p = {};
   p.alpha = alpha; p.scaled = alpha != 1.0f; p.unary = unary;
   p.W = (const __nv_bfloat16*)W; p.M = M; p.N = N; p.K = K; p.ldw = ldw;

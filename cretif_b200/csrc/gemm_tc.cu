@@ -1134,7 +1134,7 @@ extern "C" int cretif_gemm_tc(const void* A, const void* W, void* C, int c_dt, i
                               int lda, int ldw, int ldc, int accumulate, int bn, float alpha,
                               int unary, unsigned int* fault, void* stream) {
   if (M <= 0 || N <= 0) return kOk;
-  if (unary < 0 || unary > 3 || (unary && accumulate)) return kBadArgument;
+  if (unary < 0 || unary > kUnaryKinds || (unary && accumulate)) return kBadArgument;
   if (K <= 0 || K % 8 || lda % 8 || ldw % 8 || lda < K || ldw < K || ldc < N) return kBadArgument;
   if ((M + kTcBM - 1) / kTcBM > 65535) return kBadArgument;
   if (((uintptr_t)A | (uintptr_t)W | (uintptr_t)C) & 15) return kMisaligned;
@@ -1222,6 +1222,33 @@ extern "C" int cretif_gemm_tc_grouped(const void* A, const void* W, void* C, int
   if (mt * ((N + 127) / 128) >= 148)
     return launch_tc<128, kTcStore, float>(A, W, ep, M, N, K, lda, ldw, fault, st, groups * N);
   return launch_tc<64, kTcStore, float>(A, W, ep, M, N, K, lda, ldw, fault, st, groups * N);
+}
+
+// ... and C [M, N] bfloat16 = act(A W[g]^T), act a kind of unary_activation (unary = 1 + kind):
+// the first product of experts without a gate.
+extern "C" int cretif_gemm_tc_act_grouped(const void* A, const void* W, void* C, int M, int N,
+                                          int K, int lda, int ldw, int ldc, int groups,
+                                          const int* tile_group, const int* used_m_tiles,
+                                          int unary, unsigned int* fault, void* stream) {
+  if (M <= 0 || N <= 0 || groups <= 0) return kOk;
+  if (!tc_operands_ok(A, W, M, K, lda, ldw) || M % kTcBM || ldc < N || ldc % 8 || !tile_group ||
+      unary < 1 || unary > kUnaryKinds || (long long)groups * N > 0x7fffffffLL)
+    return kBadArgument;
+  if (((uintptr_t)C) & 15) return kMisaligned;
+  TcEpi ep = {};
+  ep.C = C; ep.ldc = ldc; ep.accumulate = 0;
+  ep.alpha = 1.0f; ep.scaled = 0; ep.unary = unary;
+  ep.tile_group = tile_group; ep.group_rows = N; ep.used_m_tiles = used_m_tiles;
+  const long long mt = M / kTcBM;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (mt * ((N + 255) / 256) >= 148)
+    return launch_tc<256, kTcStoreEx, __nv_bfloat16>(A, W, ep, M, N, K, lda, ldw, fault, st,
+                                                     groups * N);
+  if (mt * ((N + 127) / 128) >= 148)
+    return launch_tc<128, kTcStoreEx, __nv_bfloat16>(A, W, ep, M, N, K, lda, ldw, fault, st,
+                                                     groups * N);
+  return launch_tc<64, kTcStoreEx, __nv_bfloat16>(A, W, ep, M, N, K, lda, ldw, fault, st,
+                                                  groups * N);
 }
 
 // ... and act [M, I] = silu(A Wg[g]^T) * (A Wu[g]^T), Wgu [groups, 2 I, K] with gate and up rows

@@ -154,6 +154,29 @@ __global__ void gate_heads8_kernel(__nv_bfloat16* __restrict__ o, int ldo,
   *p = raw;
 }
 
+// A gate per channel (value size 1: every column is a head of its own), bfloat16 rows: a thread
+// takes eight channels and their eight gates.
+__global__ void gate_channels8_kernel(__nv_bfloat16* __restrict__ o, int ldo,
+                                      const float* __restrict__ g, int ldg, int width,
+                                      long long groups) {
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= groups) return;
+  const int per_row = width / 8;
+  const long long t = idx / per_row;
+  const int col = (int)(idx - t * per_row) * 8;
+  const float* gp = g + (size_t)t * ldg + col;
+  uint4* p = reinterpret_cast<uint4*>(o + (size_t)t * ldo + col);
+  uint4 raw = *p;
+  __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    const float2 f = __bfloat1622float2(h2[e]);
+    h2[e] = __floats2bfloat162_rn(f.x / (1.0f + expf(-gp[2 * e])),
+                                  f.y / (1.0f + expf(-gp[2 * e + 1])));
+  }
+  *p = raw;
+}
+
 template <typename TI, typename TO>
 __global__ void activation_kernel(const TI* __restrict__ in, int ldi, TO* __restrict__ out, int ldo,
                                   int width, long long total, int kind) {
@@ -235,6 +258,9 @@ extern "C" int cretif_gate_heads(void* o, int ldo, int dt, const float* g, int l
   cudaStream_t st = (cudaStream_t)stream;
   if (dt == kF32)
     gate_heads_kernel<float><<<blocks, 256, 0, st>>>((float*)o, ldo, g, ldg, nh, vd, total);
+  else if (dt == kBF16 && vd == 1 && nh % 8 == 0 && ldo % 8 == 0 && ((uintptr_t)o & 15) == 0)
+    gate_channels8_kernel<<<(unsigned)((total / 8 + 255) / 256), 256, 0, st>>>(
+        (__nv_bfloat16*)o, ldo, g, ldg, nh, total / 8);
   else if (dt == kBF16 && vd % 8 == 0 && ldo % 8 == 0 && ((uintptr_t)o & 15) == 0)
     gate_heads8_kernel<<<(unsigned)((total / 8 + 255) / 256), 256, 0, st>>>(
         (__nv_bfloat16*)o, ldo, g, ldg, nh, vd, total / 8);
@@ -249,7 +275,7 @@ extern "C" int cretif_gate_heads(void* o, int ldo, int dt, const float* g, int l
 extern "C" int cretif_activation(const void* in, int ldi, int in_dt, void* out, int ldo, int out_dt,
                                  int T, int width, int kind, void* stream) {
   if (T <= 0 || width <= 0) return kOk;
-  if (ldi < width || ldo < width || kind < 0 || kind > 2) return kBadArgument;
+  if (ldi < width || ldo < width || kind < 0 || kind >= kUnaryKinds) return kBadArgument;
   const long long total = (long long)T * width;
   const unsigned blocks = (unsigned)((total + 255) / 256);
   cudaStream_t st = (cudaStream_t)stream;

@@ -37,16 +37,82 @@ namespace {
 constexpr int kTile = 64;
 constexpr int kMaxExpertsPerLane = 8;            // E <= 256
 
-// Warp-wide: the `top` largest of E logits (ties: the lower index), their logistic scores as
-// weights (divided by their sum with renorm), written for token t.
-__device__ __forceinline__ void select_top(const float* logits, int E, int top, int renorm,
+// How a token's experts are chosen.  groups > 1: the experts form that many equal groups of
+// neighbours, a group's score is the sum of its two largest logistic scores, and only experts of
+// the `keep` best groups can be chosen.  renorm: the chosen scores are divided by their sum plus
+// sum_eps.
+struct RouteRule {
+  int top, renorm, groups, keep;
+  float sum_eps;
+};
+
+// Warp-wide: the `top` largest of E logits (ties: the lower index) among the experts of the groups
+// that are kept, their logistic scores as weights, written for token t.  `scratch`: E floats and
+// `groups` ints of shared memory that belong to this warp.
+__device__ __forceinline__ void select_top(const float* logits, int E, const RouteRule rule,
                                            int* __restrict__ ids, float* __restrict__ wts, int t,
-                                           int lane) {
+                                           int lane, float* scratch) {
+  const int top = rule.top, renorm = rule.renorm;
   float z[kMaxExpertsPerLane];
 #pragma unroll
   for (int m = 0; m < kMaxExpertsPerLane; ++m) {
     const int e = lane + 32 * m;
     z[m] = e < E ? logits[e] : -INFINITY;
+  }
+  if (rule.groups > 1) {
+    const int per = E / rule.groups;
+    int* kept = reinterpret_cast<int*>(scratch + E);
+    __syncwarp();
+#pragma unroll
+    for (int m = 0; m < kMaxExpertsPerLane; ++m) {
+      const int e = lane + 32 * m;
+      if (e < E) scratch[e] = 1.0f / (1.0f + expf(-z[m]));
+    }
+    for (int g = lane; g < rule.groups; g += 32) kept[g] = 0;
+    __syncwarp();
+    // lane g % 32 scores group g: its two largest scores, summed
+    float gs[kMaxExpertsPerLane];
+#pragma unroll
+    for (int m = 0; m < kMaxExpertsPerLane; ++m) {
+      const int g = lane + 32 * m;
+      gs[m] = -INFINITY;
+      if (g < rule.groups) {
+        float a = -INFINITY, b = -INFINITY;
+        for (int i = 0; i < per; ++i) {
+          const float v = scratch[g * per + i];
+          if (v > a) { b = a; a = v; } else if (v > b) { b = v; }
+        }
+        gs[m] = per > 1 ? a + b : a;
+      }
+    }
+    for (int k = 0; k < rule.keep; ++k) {
+      float best = -INFINITY;
+      int best_g = 0x7fffffff;
+#pragma unroll
+      for (int m = 0; m < kMaxExpertsPerLane; ++m) {
+        const int g = lane + 32 * m;
+        if (g < rule.groups && gs[m] > best) { best = gs[m]; best_g = g; }
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+        const int og = __shfl_xor_sync(0xffffffffu, best_g, o);
+        if (ob > best || (ob == best && og < best_g)) { best = ob; best_g = og; }
+      }
+      if (best_g == 0x7fffffff) break;
+      if ((best_g & 31) == lane) {
+#pragma unroll
+        for (int m = 0; m < kMaxExpertsPerLane; ++m)
+          if (m == (best_g >> 5)) gs[m] = -INFINITY;
+        kept[best_g] = 1;
+      }
+    }
+    __syncwarp();
+#pragma unroll
+    for (int m = 0; m < kMaxExpertsPerLane; ++m) {
+      const int e = lane + 32 * m;
+      if (e < E && !kept[e / per]) z[m] = -INFINITY;
+    }
   }
   float total = 0.f;
   float my_w = 0.f;
@@ -80,10 +146,10 @@ __device__ __forceinline__ void select_top(const float* logits, int E, int top, 
   }
   if (lane < top && lane < 32) {
     ids[(size_t)t * top + lane] = my_id;
-    wts[(size_t)t * top + lane] = renorm ? my_w / total : my_w;
+    wts[(size_t)t * top + lane] = renorm ? my_w / (total + rule.sum_eps) : my_w;
   }
   if (renorm && top > 32 && lane == 0)
-    for (int k = 32; k < top; ++k) wts[(size_t)t * top + k] /= total;
+    for (int k = 32; k < top; ++k) wts[(size_t)t * top + k] /= total + rule.sum_eps;
 }
 
 // A CTA per token: its sixteen warps take the experts in turn (a dot product each, every load of
@@ -104,8 +170,9 @@ __device__ __forceinline__ float4 ld4_as_float(const __nv_bfloat16* p) {
 template <typename T>
 __global__ void __launch_bounds__(kRouteWarps * 32)
 moe_route_kernel(const T* __restrict__ x, int ldx, const float* __restrict__ wr, int E, int H,
-                 int top, int renorm, int* __restrict__ ids, float* __restrict__ wts, int vec) {
+                 const RouteRule rule, int* __restrict__ ids, float* __restrict__ wts, int vec) {
   __shared__ float logits[kMaxExperts];
+  __shared__ float scratch[2 * kMaxExperts];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int t = blockIdx.x;
   const T* row = x + (size_t)t * ldx;
@@ -129,16 +196,18 @@ moe_route_kernel(const T* __restrict__ x, int ldx, const float* __restrict__ wr,
   }
   __syncthreads();
   if (warp != 0) return;
-  select_top(logits, E, top, renorm, ids, wts, t, lane);
+  select_top(logits, E, rule, ids, wts, t, lane, scratch);
 }
 
 // The same choice from logits that a matrix product left in memory: a warp per token.
 __global__ void __launch_bounds__(256)
-moe_topk_kernel(const float* __restrict__ logits, int ld, int E, int top, int renorm,
+moe_topk_kernel(const float* __restrict__ logits, int ld, int E, const RouteRule rule,
                 int* __restrict__ ids, float* __restrict__ wts, int T) {
+  __shared__ float scratch[8][2 * kMaxExperts];
   const int t = blockIdx.x * 8 + (threadIdx.x >> 5);
   if (t >= T) return;
-  select_top(logits + (size_t)t * ld, E, top, renorm, ids, wts, t, threadIdx.x & 31);
+  select_top(logits + (size_t)t * ld, E, rule, ids, wts, t, threadIdx.x & 31,
+             scratch[threadIdx.x >> 5]);
 }
 
 // tile: rows of a tile; padded: every expert's rows start at a multiple of `tile` (the sorted
@@ -218,7 +287,8 @@ __device__ __forceinline__ TileRows tile_rows(const int* tile_expert, const int*
   return tr;
 }
 
-// mode 0: gate|up with the activation; mode 1: plain product into float32 rows.
+// mode 0: gate|up with the activation; mode 1: plain product into float32 rows; mode 2 + k: an
+// expert without a gate, C = act_k(A W^T) with kind k of unary_activation, rows as in mode 0.
 // scale_at: 0 none, 1 the router weight scales the sums of mode 0 (the expert's input),
 // 2 it scales the rows of mode 1 (the expert's output).
 template <typename TA, typename TW>
@@ -242,7 +312,7 @@ moe_gemm_simt_kernel(const TA* __restrict__ A, int lda, const TW* __restrict__ W
   const TW* We = W + (size_t)tr.expert * w_rows * K;
   // the row of A that the loader thread fetches
   int a_src = -1;
-  if (lrow < tr.rows) a_src = mode == 0 ? order[tr.row0 + lrow] / top : tr.row0 + lrow;
+  if (lrow < tr.rows) a_src = mode != 1 ? order[tr.row0 + lrow] / top : tr.row0 + lrow;
   const int wn = n0 + lrow;
   float acc[2][TM][TN];
 #pragma unroll
@@ -294,6 +364,9 @@ moe_gemm_simt_kernel(const TA* __restrict__ A, int lda, const TW* __restrict__ W
         const float sg = scale_at == 1 ? s : 1.f;
         const float g = acc[0][i][j] * sg, u = acc[1][i][j] * sg;
         reinterpret_cast<TA*>(Cv)[(size_t)r * ldc + n] = from_float<TA>(g / (1.0f + expf(-g)) * u);
+      } else if (mode >= 2) {
+        reinterpret_cast<TA*>(Cv)[(size_t)r * ldc + n] = from_float<TA>(
+            unary_activation(acc[0][i][j] * (scale_at == 1 ? s : 1.f), mode - 2));
       } else {
         reinterpret_cast<float*>(Cv)[(size_t)r * ldc + n] =
             acc[0][i][j] * (scale_at == 2 ? s : 1.f);
@@ -330,7 +403,7 @@ moe_gemm_mma_kernel(const __nv_bfloat16* __restrict__ A, int lda,
   const int wm = (warp >> 1) * 32, wn = (warp & 1) * 32;
   const int tid = (int)threadIdx.x;
   if (tid < kTile)
-    src_row[tid] = tid < tr.rows ? (mode == 0 ? order[tr.row0 + tid] / top : tr.row0 + tid) : -1;
+    src_row[tid] = tid < tr.rows ? (mode != 1 ? order[tr.row0 + tid] / top : tr.row0 + tid) : -1;
   __syncthreads();
   wmma::fragment<wmma::accumulator, 16, 16, 16, float> acc[2][2][2];
 #pragma unroll
@@ -411,6 +484,9 @@ moe_gemm_mma_kernel(const __nv_bfloat16* __restrict__ A, int lda,
       const float g = Cs[0][warp][lane][c] * sg, u = Cs[1][warp][lane][c] * sg;
       reinterpret_cast<__nv_bfloat16*>(Cv)[(size_t)r * ldc + n] =
           __float2bfloat16_rn(silu_bf16_path(g) * u);
+    } else if (mode >= 2) {
+      reinterpret_cast<__nv_bfloat16*>(Cv)[(size_t)r * ldc + n] = __float2bfloat16_rn(
+          unary_activation(Cs[0][warp][lane][c] * (scale_at == 1 ? s : 1.f), mode - 2));
     } else {
       reinterpret_cast<float*>(Cv)[(size_t)r * ldc + n] =
           Cs[0][warp][lane][c] * (scale_at == 2 ? s : 1.f);
@@ -422,7 +498,8 @@ moe_gemm_mma_kernel(const __nv_bfloat16* __restrict__ A, int lda,
 // columns of ONE pair, streams its expert's rows for them once (16-byte loads, all of a row's in
 // flight together) against the pair's input row held in shared memory; warp w takes columns
 // 2w and 2w + 1.  mode 0: C[p, n] = silu(s g) (s u) from the gate row n and the up row N + n;
-// mode 1: C[p, n] = the product (times s with scale_at 2), float32.
+// mode 1: C[p, n] = the product (times s with scale_at 2), float32; mode 2 + k: C[p, n] =
+// act_k(s * the product) from row n of an expert without a gate.
 template <typename T>
 __global__ void __launch_bounds__(256)
 moe_gemv_kernel(const T* __restrict__ A, int lda, const T* __restrict__ W, void* Cv, int ldc, int N,
@@ -433,7 +510,7 @@ moe_gemv_kernel(const T* __restrict__ A, int lda, const T* __restrict__ W, void*
   const int p = blockIdx.y;
   const int e = ids[p];
   const float s = scale_at ? wts[p] : 1.f;
-  const T* arow = A + (size_t)(mode == 0 ? p / top : p) * lda;
+  const T* arow = A + (size_t)(mode != 1 ? p / top : p) * lda;
   if (vec) {
     const int bytes = K * (int)sizeof(T);               // a multiple of 16
     const unsigned char* src = reinterpret_cast<const unsigned char*>(arow);
@@ -471,6 +548,10 @@ moe_gemv_kernel(const T* __restrict__ A, int lda, const T* __restrict__ W, void*
       const float g = dot(We + (size_t)n * K) * sg, u = dot(We + ((size_t)N + n) * K) * sg;
       if (lane == 0)
         reinterpret_cast<T*>(Cv)[(size_t)p * ldc + n] = from_float<T>(g / (1.0f + expf(-g)) * u);
+    } else if (mode >= 2) {
+      const float v = dot(We + (size_t)n * K) * (scale_at == 1 ? s : 1.f);
+      if (lane == 0)
+        reinterpret_cast<T*>(Cv)[(size_t)p * ldc + n] = from_float<T>(unary_activation(v, mode - 2));
     } else {
       const float v = dot(We + (size_t)n * K) * (scale_at == 2 ? s : 1.f);
       if (lane == 0) reinterpret_cast<float*>(Cv)[(size_t)p * ldc + n] = v;
@@ -498,32 +579,44 @@ moe_combine_kernel(const float* __restrict__ rows, int ld, const int* __restrict
 
 using namespace cretif;
 
+// groups <= 1: no groups.  Else the experts divide into the groups evenly and the groups that
+// are kept hold `top` experts at least.
+static bool route_rule_ok(int E, int top, int groups, int keep) {
+  if (groups <= 1) return true;
+  return E % groups == 0 && keep >= 1 && keep <= groups && (long long)keep * (E / groups) >= top;
+}
+
 extern "C" int cretif_moe_route(const void* x, int x_dt, int ldx, const float* router_w, int E,
-                                int H, int top, int renorm, int* ids, float* wts, int T,
-                                void* stream) {
+                                int H, int top, int renorm, int groups, int keep, float sum_eps,
+                                int* ids, float* wts, int T, void* stream) {
   if (T <= 0) return kOk;
   if (E <= 0 || E > 32 * kMaxExpertsPerLane || H <= 0 || top <= 0 || top > E || ldx < H)
     return kBadArgument;
+  if (!route_rule_ok(E, top, groups, keep)) return kBadArgument;
+  const RouteRule rule{top, renorm, groups, keep, sum_eps};
   cudaStream_t st = (cudaStream_t)stream;
   const int vec = H % 4 == 0 && ldx % 4 == 0 && (((uintptr_t)x | (uintptr_t)router_w) & 15) == 0;
   if (x_dt == kF32)
     moe_route_kernel<float><<<T, kRouteWarps * 32, 0, st>>>((const float*)x, ldx, router_w, E, H,
-                                                            top, renorm, ids, wts, vec);
+                                                            rule, ids, wts, vec);
   else if (x_dt == kBF16)
     moe_route_kernel<__nv_bfloat16><<<T, kRouteWarps * 32, 0, st>>>(
-        (const __nv_bfloat16*)x, ldx, router_w, E, H, top, renorm, ids, wts, vec);
+        (const __nv_bfloat16*)x, ldx, router_w, E, H, rule, ids, wts, vec);
   else
     return kBadDType;
   return launch_status();
 }
 
 // ids/wts from logits [T, ld >= E] that a matrix product computed.
-extern "C" int cretif_moe_topk(const float* logits, int ld, int E, int top, int renorm, int* ids,
-                               float* wts, int T, void* stream) {
+extern "C" int cretif_moe_topk(const float* logits, int ld, int E, int top, int renorm, int groups,
+                               int keep, float sum_eps, int* ids, float* wts, int T,
+                               void* stream) {
   if (T <= 0) return kOk;
   if (E <= 0 || E > kMaxExperts || top <= 0 || top > E || ld < E) return kBadArgument;
-  moe_topk_kernel<<<(unsigned)((T + 7) / 8), 256, 0, (cudaStream_t)stream>>>(logits, ld, E, top,
-                                                                             renorm, ids, wts, T);
+  if (!route_rule_ok(E, top, groups, keep)) return kBadArgument;
+  const RouteRule rule{top, renorm, groups, keep, sum_eps};
+  moe_topk_kernel<<<(unsigned)((T + 7) / 8), 256, 0, (cudaStream_t)stream>>>(logits, ld, E, rule,
+                                                                             ids, wts, T);
   return launch_status();
 }
 
@@ -561,6 +654,7 @@ extern "C" int cretif_moe_gather_rows(const void* x, int ldx, void* xs, int lds,
 }
 
 // mode 0: A [tokens, K] (row of pair p: p / top), W [E, 2N, K], C [P, N] in A's element type.
+// mode 2 + k: the same rows, W [E, N, K], C = act_k(product) (k: a kind of unary_activation).
 // mode 1: A [P, K] sorted rows, W [E, N, K], C [P, N] float32.  use_mma: the tensor-core body
 // (bfloat16 only).
 extern "C" int cretif_moe_gemm(const void* A, int a_dt, int lda, const void* W, int w_dt, void* C,
@@ -569,7 +663,7 @@ extern "C" int cretif_moe_gemm(const void* A, int a_dt, int lda, const void* W, 
                                const int* tile_expert, const int* tile_row0, int max_tiles,
                                int use_mma, void* stream) {
   if (max_tiles <= 0) return kOk;
-  if (N <= 0 || K <= 0 || lda < K || ldc < N || top <= 0 || mode < 0 || mode > 1 ||
+  if (N <= 0 || K <= 0 || lda < K || ldc < N || top <= 0 || mode < 0 || mode >= 2 + kUnaryKinds ||
       scale_at < 0 || scale_at > 2 || max_tiles > 65535 || a_dt != w_dt)
     return kBadArgument;
   cudaStream_t st = (cudaStream_t)stream;
@@ -614,7 +708,7 @@ extern "C" int cretif_moe_gemv(const void* A, int a_dt, int lda, const void* W, 
                                int ldc, int N, int K, int top, int mode, int scale_at,
                                const int* ids, const float* wts, int P, void* stream) {
   if (P <= 0) return kOk;
-  if (N <= 0 || K <= 0 || lda < K || ldc < N || top <= 0 || mode < 0 || mode > 1 ||
+  if (N <= 0 || K <= 0 || lda < K || ldc < N || top <= 0 || mode < 0 || mode >= 2 + kUnaryKinds ||
       scale_at < 0 || scale_at > 2 || P > 65535 || a_dt != w_dt)
     return kBadArgument;
   const size_t esz = a_dt == kF32 ? 4 : 2;

@@ -407,6 +407,76 @@ def headnorm_rope_kv_append(proj, bias, wq, wk, eps: float, cos, sin, pairing: i
         int(write_cache), T, _p(fault), _stream()), "headnorm_rope_kv_append")
 
 
+def latent_in(proj, q_rank: int, rank: int, rot: int, wq, wc, eps: float, cos, sin, pairing: int,
+              tok_pos, tok_seq, seq_slot, cq_out, table=None, kc=None, block_tokens: int = 64,
+              write_cache: bool = True, fault=None) -> None:
+    """``proj`` rows [cq (q_rank) | c (rank) | kr (rot) | ...] (float32, or the cache's type):
+    cq and c to unit RMS times ``wq`` / ``wc`` (float32), kr rotated by the position; cq to
+    ``cq_out`` [T, q_rank] (``q_rank`` 0: no query latent), [c | kr] into the token's row of the
+    key cache ``kc`` [blocks, 1, block_tokens, rank + rot]."""
+    _need(proj, "proj", dim=2); _need(wc, "wc", torch.float32, 1)
+    T = proj.shape[0]
+    dt = kc.dtype if kc is not None else cq_out.dtype
+    if proj.dtype not in (torch.float32, dt) or proj.shape[1] < q_rank + rank + rot:
+        raise KernelError("latent_in: proj is float32 or of the cache's type and holds "
+                          "[cq | c | kr]")
+    if wc.numel() != rank or not wc.is_contiguous():
+        raise KernelError("latent_in: the latent's norm weight has `rank` numbers")
+    if q_rank:
+        _need(wq, "wq", torch.float32, 1); _need(cq_out, "cq_out", dt, 2)
+        if wq.numel() != q_rank or cq_out.shape[0] != T or cq_out.shape[1] < q_rank \
+                or not wq.is_contiguous():
+            raise KernelError("latent_in: the query latent's weight and output have q_rank columns")
+    if rot:
+        _need(cos, "cos", torch.float32, 2); _need(sin, "sin", torch.float32, 2)
+        if cos.shape[1] != rot // 2 or not cos.is_contiguous() or not sin.is_contiguous():
+            raise KernelError("latent_in: cos/sin must be contiguous [positions, rot/2]")
+    else:
+        cos = sin = None
+    if write_cache:
+        _need(table, "table", torch.int32, 2); _need(kc, "k cache", dt, 4)
+        if tuple(kc.shape[1:]) != (1, block_tokens, rank + rot) or not kc.is_contiguous():
+            raise KernelError(f"latent_in: the cache must be contiguous [blocks, 1, "
+                              f"{block_tokens}, {rank + rot}]")
+    if fault is None:
+        fault = fault_word(proj.device)
+    _check(lib().cretif_latent_in(
+        _p(proj), _rows(proj, "proj"), _dt(proj), q_rank, rank, rot, _p(wq), _p(wc),
+        ctypes.c_float(eps), _p(cos), _p(sin), pairing, _p(tok_pos), _p(tok_seq), _p(seq_slot),
+        _p(cq_out), _rows(cq_out, "cq_out") if q_rank else 0, _DT[dt], _p(table),
+        table.stride(0) if table is not None else 0, _p(kc), block_tokens, int(write_cache), T,
+        _p(fault), _stream()), "latent_in")
+
+
+def rope_heads(q, nh: int, d: int, rot: int, cos, sin, pairing: int, tok_pos, out, off: int) -> None:
+    """``q`` [T, nh·(d + rot)]: the last ``rot`` channels of every head, rotated by the token's
+    position, go to ``out[t, h, off : off + rot]`` (``out`` [T, nh, width >= off + rot], of the
+    compute type; ``q`` float32 or of that type)."""
+    _need(q, "q", dim=2); _need(out, "out", dim=3)
+    T = q.shape[0]
+    if (q.shape[1] < nh * (d + rot) or out.shape[0] != T or out.shape[1] != nh
+            or out.shape[2] < off + rot or out.stride(2) != 1
+            or q.dtype not in (torch.float32, out.dtype)):
+        raise KernelError("rope_heads: sizes or element types do not fit")
+    if rot == 0:
+        return
+    _need(cos, "cos", torch.float32, 2); _need(sin, "sin", torch.float32, 2)
+    if cos.shape[1] != rot // 2 or not cos.is_contiguous() or not sin.is_contiguous():
+        raise KernelError("rope_heads: cos/sin must be contiguous [positions, rot/2]")
+    _check(lib().cretif_rope_heads(
+        _p(q), _rows(q, "q"), _dt(q), nh, d, rot, _p(cos), _p(sin), pairing, _p(tok_pos), _p(out),
+        out.stride(0), out.stride(1), off, _dt(out), T, _stream()), "rope_heads")
+
+
+def rmsnorm_rows(x, weight, eps: float) -> None:
+    """``x <- x / sqrt(mean(x²) + eps) * weight`` in place on float32 rows."""
+    _need(x, "x", torch.float32, 2); _need(weight, "weight", torch.float32, 1)
+    if weight.numel() != x.shape[1] or not weight.is_contiguous():
+        raise KernelError("rmsnorm_rows: a weight per column")
+    _check(lib().cretif_rmsnorm_rows(_p(x), _rows(x, "x"), _p(weight), x.shape[0], x.shape[1],
+                                     ctypes.c_float(eps), _stream()), "rmsnorm_rows")
+
+
 def gate_heads(o, g, nh: int, vd: int) -> None:
     """``o[t, h, :] *= sigmoid(g[t, h])``; ``g`` float32 [T, >= nh] (columns of a projection)."""
     _need(o, "o", dim=2); _need(g, "g", torch.float32, 2)
@@ -416,12 +486,12 @@ def gate_heads(o, g, nh: int, vd: int) -> None:
                                    o.shape[0], _stream()), "gate_heads")
 
 
-ACTIVATIONS = {"relu2": 0, "gelu_tanh": 1, "silu": 2}
+ACTIVATIONS = {"relu2": 0, "gelu_tanh": 1, "silu": 2, "gelu": 3}
 
 
 def activation(x, out, kind: str) -> None:
     """``out = act(x)`` element by element: ``relu2`` (the square of relu), ``gelu_tanh``,
-    ``silu``; ``x`` float32 or of ``out``'s type."""
+    ``silu``, ``gelu`` (the exact form, with the error function); ``x`` float32 or of ``out``'s type."""
     _need(x, "x", dim=2); _need(out, "out", dim=2)
     if kind not in ACTIVATIONS:
         raise KernelError(f"activation: {kind!r} is none of {sorted(ACTIVATIONS)}")
@@ -676,8 +746,18 @@ def moe_max_tiles(pairs: int, experts: int) -> int:
     return -(-pairs // MOE_TILE) + experts
 
 
-def moe_route(x, router_w, top: int, ids, wts, renorm: bool = False) -> None:
-    """ids/wts [T, top]: the ``top`` experts with the largest sigmoid(router_w · x) per token."""
+def _route_rule(E: int, top: int, groups: int, keep: int) -> None:
+    if groups > 1 and (E % groups or not 1 <= keep <= groups or keep * (E // groups) < top):
+        raise KernelError(f"routing: {E} experts do not form {groups} equal groups of which "
+                          f"{keep} hold {top} experts")
+
+
+def moe_route(x, router_w, top: int, ids, wts, renorm: bool = False, groups: int = 0,
+              keep: int = 0, sum_eps: float = 0.0) -> None:
+    """ids/wts [T, top]: the ``top`` experts with the largest sigmoid(router_w · x) per token.
+    ``groups`` > 1: the experts form that many equal groups of neighbours, a group's score is
+    the sum of its two largest scores, and only experts of the ``keep`` best groups can be
+    chosen.  ``renorm``: the weights are divided by (their sum + ``sum_eps``)."""
     _need(x, "x", dim=2); _need(router_w, "router_w", torch.float32, 2)
     _need(ids, "ids", torch.int32, 2); _need(wts, "wts", torch.float32, 2)
     T, H = x.shape
@@ -687,11 +767,14 @@ def moe_route(x, router_w, top: int, ids, wts, renorm: bool = False) -> None:
         raise KernelError("moe_route: sizes do not fit")
     if not 0 < top <= E or E > 256:
         raise KernelError(f"moe_route: {top} of {E} experts (at most 256) cannot be chosen")
+    _route_rule(E, top, groups, keep)
     _check(lib().cretif_moe_route(_p(x), _dt(x), _rows(x, "x"), _p(router_w), E, H, top,
-                                  int(renorm), _p(ids), _p(wts), T, _stream()), "moe_route")
+                                  int(renorm), int(groups), int(keep), ctypes.c_float(sum_eps),
+                                  _p(ids), _p(wts), T, _stream()), "moe_route")
 
 
-def moe_topk(logits, top: int, ids, wts, renorm: bool = False) -> None:
+def moe_topk(logits, top: int, ids, wts, renorm: bool = False, groups: int = 0, keep: int = 0,
+             sum_eps: float = 0.0) -> None:
     """``moe_route``'s choice from router logits [T, E] (float32) that a matrix product left."""
     _need(logits, "logits", torch.float32, 2); _need(ids, "ids", torch.int32, 2)
     _need(wts, "wts", torch.float32, 2)
@@ -699,7 +782,9 @@ def moe_topk(logits, top: int, ids, wts, renorm: bool = False) -> None:
     if (tuple(ids.shape) != (T, top) or tuple(wts.shape) != (T, top) or not ids.is_contiguous()
             or not wts.is_contiguous() or not 0 < top <= E or E > 256):
         raise KernelError("moe_topk: sizes do not fit")
-    _check(lib().cretif_moe_topk(_p(logits), _rows(logits, "logits"), E, top, int(renorm), _p(ids),
+    _route_rule(E, top, groups, keep)
+    _check(lib().cretif_moe_topk(_p(logits), _rows(logits, "logits"), E, top, int(renorm),
+                                 int(groups), int(keep), ctypes.c_float(sum_eps), _p(ids),
                                  _p(wts), T, _stream()), "moe_topk")
 
 
@@ -721,16 +806,24 @@ def moe_group(ids, experts: int, offsets, place, order, tile_expert, tile_row0) 
            "moe_group")
 
 
+def moe_act_mode(kind: str) -> int:
+    """The ``mode`` of ``moe_gemm`` / ``moe_gemv`` for the first product of experts without a
+    gate whose activation is ``kind`` (a key of ACTIVATIONS)."""
+    return 2 + ACTIVATIONS[kind]
+
+
 def moe_gemm(a, w, c, top: int, mode: int, scale_at: int, wts, order, offsets, tile_expert,
              tile_row0) -> None:
     """Grouped product over the sorted rows.  mode 0: ``a`` [tokens, K], ``w`` [E, 2N, K]
     (gate rows then up rows), ``c`` [P, N] = silu(s g)(s u) (scale_at 1) or silu(g) u; mode 1:
-    ``a`` [P, K] sorted rows, ``w`` [E, N, K], ``c`` [P, N] float32 (scale_at 2: times s)."""
+    ``a`` [P, K] sorted rows, ``w`` [E, N, K], ``c`` [P, N] float32 (scale_at 2: times s);
+    mode ``moe_act_mode(kind)``: experts without a gate, ``a`` as in mode 0, ``w`` [E, N, K],
+    ``c`` = act(s · product)."""
     _need(a, "a", dim=2); _need(w, "w", a.dtype, 3); _need(c, "c", dim=2)
     K = a.shape[1]
     N = c.shape[1]
     if (w.shape[2] != K or w.shape[1] != (2 * N if mode == 0 else N) or not w.is_contiguous()
-            or c.dtype != (a.dtype if mode == 0 else torch.float32) or c.shape[0] != order.numel()):
+            or c.dtype != (a.dtype if mode != 1 else torch.float32) or c.shape[0] != order.numel()):
         raise KernelError("moe_gemm: sizes or element types do not fit")
     use_mma = int(a.dtype == torch.bfloat16 and not _moe_simt_only)
     _check(lib().cretif_moe_gemm(
@@ -746,7 +839,7 @@ def moe_gemv(a, w, c, top: int, mode: int, scale_at: int, ids, wts) -> None:
     _need(ids, "ids", torch.int32); _need(wts, "wts", torch.float32)
     K, N, P = a.shape[1], c.shape[1], ids.numel()
     if (w.shape[2] != K or w.shape[1] != (2 * N if mode == 0 else N) or not w.is_contiguous()
-            or c.dtype != (a.dtype if mode == 0 else torch.float32) or c.shape[0] != P
+            or c.dtype != (a.dtype if mode != 1 else torch.float32) or c.shape[0] != P
             or wts.numel() != P or not ids.is_contiguous() or not wts.is_contiguous()):
         raise KernelError("moe_gemv: sizes or element types do not fit")
     _check(lib().cretif_moe_gemv(
@@ -789,12 +882,12 @@ def moe_gather_rows(x, xs, place, wts, top: int) -> None:
            "moe_gather_rows")
 
 
-def moe_tc_supported(x, w_gu, w_down) -> bool:
+def moe_tc_supported(x, w_gu, w_down, gated: bool = True) -> bool:
     """Whether the grouped tensor-core products take these operands (bfloat16, widths that are
     multiples of 8, an expert width that is a multiple of 64)."""
     K, F = x.shape[1], w_down.shape[2]
     return (x.dtype == torch.bfloat16 and w_gu.dtype == torch.bfloat16 and K % 8 == 0
-            and F % 64 == 0 and not _moe_simt_only)
+            and F % (64 if gated else 8) == 0 and not _moe_simt_only)
 
 
 def gemm_tc_silu_grouped(xs, w_gu, act, tile_expert, used) -> None:
@@ -811,6 +904,21 @@ def gemm_tc_silu_grouped(xs, w_gu, act, tile_expert, used) -> None:
     _check(lib().cretif_gemm_tc_silu_grouped(
         _p(xs), _p(w_gu), _p(act), M, F, K, _rows(xs, "xs"), K, E, _p(tile_expert), _p(used),
         _p(fault_word(xs.device)), _stream()), "gemm_tc_silu_grouped")
+
+
+def gemm_tc_act_grouped(a, w, c, tile_expert, used, kind: str) -> None:
+    """c (bfloat16) = act(a W[e]ᵀ) tile by tile; ``w`` [E, N, K], ``kind`` a key of ACTIVATIONS."""
+    _need(a, "a", torch.bfloat16, 2); _need(w, "w", torch.bfloat16, 3)
+    _need(c, "c", torch.bfloat16, 2)
+    M, K = a.shape
+    E, N = w.shape[0], w.shape[1]
+    if (M % MOE_TC_TILE or tuple(c.shape) != (M, N) or w.shape[2] != K or not w.is_contiguous()
+            or tile_expert.numel() < M // MOE_TC_TILE):
+        raise KernelError("gemm_tc_act_grouped: sizes do not fit")
+    _check(lib().cretif_gemm_tc_act_grouped(
+        _p(a), _p(w), _p(c), M, N, K, _rows(a, "a"), K, _rows(c, "c"), E, _p(tile_expert),
+        _p(used), 1 + ACTIVATIONS[kind], _p(fault_word(a.device)), _stream()),
+        "gemm_tc_act_grouped")
 
 
 def gemm_tc_grouped(a, w, c, tile_expert, used) -> None:
@@ -845,8 +953,11 @@ def moe_combine(rows, place, top: int, y, wts=None) -> None:
 # ------------------------------------------------------------------ attention
 def attn_simt(q, out, kc, vc, table, tok_pos, tok_seq, seq_slot, nh: int, nkv: int, hd: int,
               scale: float, window: int, block_tokens: int, sink=None, vd: int = 0, bias=None,
-              bias_edges=None) -> None:
-    """``sink`` (float32 [heads], optional): exp(sink_h) joins head h's softmax denominator
+              bias_edges=None, slope=None) -> None:
+    """``window`` > 0: a sliding window of that many keys; < 0: chunks of ``-window`` positions
+    counted from 0, a query sees the keys of its own chunk; 0: every earlier key.  ``slope``
+    (float32 [heads], optional): the key n positions back has ``slope[h] * n`` taken off its
+    scaled score.  ``sink`` (float32 [heads], optional): exp(sink_h) joins head h's softmax denominator
     without a key or a value.  ``vd``: size of a value head when it is not ``hd``.  ``bias``
     (float32 [rows, heads]) with ``bias_edges`` (int32 [rows], ascending from 0): the key n
     positions back adds ``bias[r, h]`` to its scaled score, r the last row with edge <= n."""
@@ -875,11 +986,15 @@ def attn_simt(q, out, kc, vc, table, tok_pos, tok_seq, seq_slot, nh: int, nkv: i
                 or not bias_edges.is_contiguous() or not 0 < rows <= 1024):
             raise KernelError("attention: the distance bias is [rows <= 1024, heads] with one "
                               "edge per row")
+    if slope is not None:
+        _need(slope, "slope", torch.float32, 1)
+        if slope.numel() != nh or not slope.is_contiguous():
+            raise KernelError("attention: the slope has one number per query head")
     _check(lib().cretif_attn_simt(
         _p(q), _rows(q, "q"), _p(out), _rows(out, "out"), _dt(q), _p(kc), _p(vc), _p(table),
         table.stride(0), _p(tok_pos), _p(tok_seq), _p(seq_slot), nh, nkv, hd,
         ctypes.c_float(scale), window, block_tokens, T, _p(sink), vd, _p(bias), _p(bias_edges),
-        rows, _stream()), "attn_simt")
+        rows, _p(slope), _stream()), "attn_simt")
 
 
 # ------------------------------------------------------------------ sampling

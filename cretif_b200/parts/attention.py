@@ -25,6 +25,13 @@ beyond that rows spaced by the logarithm up to ``far``), ``value_dim`` (values o
 size than the keys) and ``own_kv: False`` (no key and value tensors: the layer reads the keys
 and values that another schedule entry stores, with queries, bias and everything else of its
 own).  One kernel does convolution, head norm, gain and the cache write.
+
+``chunk`` (an integer) replaces the sliding window by chunks: a query sees the earlier keys of
+its own run of ``chunk`` positions, runs counted from position 0 of the sequence.
+``distance_slope`` (``{"exponent": x}``) takes ``slope_h * (i - j)`` off the scaled score of key j
+for query i, with ``slope_h = 2^(-x (h + 1) / heads)``.  Both belong to the family whose
+projections are handled head by head, which also serves a layer without key and value tensors of
+its own (``own_kv: False``).
 """
 from __future__ import annotations
 
@@ -83,19 +90,35 @@ def distance_edges(rows: int, far: float):
 FAST_BIAS_MAX_DISTANCES = 4096
 
 
+def slope_table(slopes, distances: int):
+    """A slope by distance as the tensor-core kernels take a bias: (near [heads, distances],
+    far [heads]), times log2 e; ``far`` stands for every distance from ``distances`` on, which a
+    window or a chunk of at most that many keys never shows."""
+    log2e = 1.4426950408889634
+    n = torch.arange(distances, dtype=torch.float64, device=slopes.device)
+    near = (-(slopes.double()[:, None] * n[None, :]) * log2e).float().contiguous()
+    far = (-(slopes.double() * distances) * log2e).float().contiguous()
+    return near, far
+
+
 def run_attention(q, o, ctx, kv, nh, nkv, hd, scale, window, dtype, sink=None, vd=0, bias=None,
-                  bias_edges=None, bias_dense=None):
+                  bias_edges=None, bias_dense=None, slope=None):
     """Causal (windowed) attention of the step's queries ``q`` [T, nh·hd] over the cache view
     ``kv`` into ``o``, with the kernel that fits the step: the decode kernels when every
     sequence brings one token, the prompt kernel otherwise, the plain kernel for float32 and
     for whatever the fast ones do not take (values of another size than the keys, a bias whose
     rows reach farther than the fast kernels' table).  ``bias`` [rows, heads] with
     ``bias_edges`` is the bias by distance as the plain kernel takes it, ``bias_dense`` =
-    (near [heads, n_far], far [heads]), times log2 e, as the tensor-core kernels do."""
+    (near [heads, n_far], far [heads]), times log2 e, as the tensor-core kernels do.  ``window``
+    below zero stands for chunks of ``-window`` positions.  ``slope`` [heads]: a multiple of the
+    distance taken off the scores; the fast kernels take it as ``bias_dense`` (made by
+    ``slope_table`` when the mask bounds the distance), the plain kernel as it is."""
     vd = vd or hd
+    biased = bias is not None or slope is not None
     fast = (not _force_plain and dtype == torch.bfloat16 and (sink is None or hd <= 128)
-            and vd == hd and (bias is None or (bias_dense is not None and hd <= 128)))
-    near, far = bias_dense if (bias is not None and bias_dense is not None) else (None, None)
+            and vd == hd and not (bias is not None and slope is not None)
+            and (not biased or (bias_dense is not None and hd <= 128)))
+    near, far = bias_dense if (biased and bias_dense is not None) else (None, None)
     if fast:
         if ctx.is_decode and ops.attn_decode_supported(hd, kv.block_tokens, min(nh // nkv, 8)) \
                 and (nh // nkv <= 8 or nkv == 1):
@@ -119,7 +142,7 @@ def run_attention(q, o, ctx, kv, nh, nkv, hd, scale, window, dtype, sink=None, v
             return
     ops.attn_simt(q, o, kv.k, kv.v, kv.table, ctx.tok_pos, ctx.tok_seq, ctx.seq_slot,
                   nh, nkv, hd, scale, window, kv.block_tokens, sink=sink, vd=vd, bias=bias,
-                  bias_edges=bias_edges)
+                  bias_edges=bias_edges, slope=slope)
 
 
 @register_part("mixer", "attention")
@@ -140,6 +163,11 @@ class Attention(Part):
         self.hd = int(params["head_dim"])
         self.scale = float(params["scale"])
         self.window = int(params.get("window", 0))
+        self.chunk = int(params.get("chunk") or 0)
+        if self.chunk < 0 or self.window < 0 or (self.chunk and self.window):
+            raise ValueError("attention: give a sliding `window` or a `chunk`, not both, and "
+                             "neither below zero")
+        self.mask = -self.chunk if self.chunk else self.window     # as the kernels take it
         if self.nh <= 0 or self.nkv <= 0 or self.nh % self.nkv:
             raise ValueError(f"attention: {self.nh} heads cannot share {self.nkv} key/value heads")
         if not 1 <= self.hd <= 512:
@@ -173,10 +201,13 @@ class Attention(Part):
         self.bias_names = params.get("bias")
         self.head_gate = params.get("head_gate")
         # the family that norms head by head without a convolution
+        self.slope_spec = params.get("distance_slope")
+        self.slope = None
         self.headwise = self.conv is None and bool(
-            self.bias_names or self.head_gate or self.head_norm or self.vd != self.hd)
+            self.bias_names or self.head_gate or self.head_norm or self.vd != self.hd
+            or self.chunk or self.slope_spec or not self.own_kv)
         extras = [k for k in ("query_gain", "distance_bias") if params.get(k)] \
-            + ([] if self.own_kv else ["own_kv"]) \
+            + ([] if self.own_kv or self.headwise else ["own_kv"]) \
             + ([] if self.headwise else
                [k for k in ("head_norm",) if params.get(k)]
                + (["value_dim"] if self.vd != self.hd else []))
@@ -240,8 +271,9 @@ class Attention(Part):
         if params.get("bias"):
             b = params["bias"]
             out["q_bias"] = (b["q"], WeightSpec((q,), init=(0.0, 0.1)))
-            out["k_bias"] = (b["k"], WeightSpec((kv,), init=(0.0, 0.1)))
-            out["v_bias"] = (b["v"], WeightSpec((vdim,), init=(0.0, 0.1)))
+            if own:
+                out["k_bias"] = (b["k"], WeightSpec((kv,), init=(0.0, 0.1)))
+                out["v_bias"] = (b["v"], WeightSpec((vdim,), init=(0.0, 0.1)))
         hn = params.get("head_norm")
         if hn and not conv and hn.get("q"):
             out["q_head_norm"] = (hn["q"], WeightSpec((params["head_dim"],), init=(1.0, 0.1)))
@@ -258,12 +290,15 @@ class Attention(Part):
         if self.head_gate:
             stacked.append(tensors["head_gate"])              # rows [q | k | v | gates | zeros]
             self.w_qkv = self._stacked(stacked)
+        elif self.headwise:
+            self.w_qkv = self._stacked(stacked)               # rows [q | k | v | zeros]
         else:
             self.w_qkv = self._matrix(torch.cat(stacked, dim=0))
         self.in_bias = self.q_head_w = self.k_head_w = None
         if self.bias_names:
-            self.in_bias = self._vector32(torch.cat([tensors["q_bias"], tensors["k_bias"],
-                                                     tensors["v_bias"]], dim=0))
+            self.in_bias = self._vector32(torch.cat(
+                [tensors["q_bias"]] + ([tensors["k_bias"], tensors["v_bias"]]
+                                       if self.own_kv else []), dim=0))
         if "q_head_norm" in tensors:
             self.q_head_w = self._vector32(tensors["q_head_norm"])
             self.k_head_w = self._vector32(tensors["k_head_norm"])
@@ -283,6 +318,16 @@ class Attention(Part):
                 near = self.bias[torch.from_numpy(row_of).to(self.device)].t().contiguous()
                 self.bias_dense = ((near * log2e).contiguous(),
                                    (self.bias[-1] * log2e).contiguous())
+        if self.slope_spec is not None:
+            x = float(self.slope_spec["exponent"])
+            hs = torch.arange(1, self.nh + 1, dtype=torch.float64)
+            self.slope = self._vector32(2.0 ** (-x * hs / self.nh))
+            # a window or a chunk bounds the distance: the tensor-core kernels then take the
+            # slope as a dense table of that many distances
+            span = self.chunk or self.window
+            if (self.bias is None and 1 <= span <= FAST_BIAS_MAX_DISTANCES
+                    and self.dtype == torch.bfloat16):
+                self.bias_dense = slope_table(self.slope, span)
         if self.params.get("fixed_sink") is not None:
             self.sink = torch.full((self.nh,), float(self.params["fixed_sink"]),
                                    dtype=torch.float32, device=self.device)
@@ -300,6 +345,8 @@ class Attention(Part):
             self.position.prepare(max_positions)
 
     def cache_request(self):
+        # (a chunked mask keeps every block: another layer may read these keys with a mask of
+        # its own)
         kv = KVRequest(self.nkv, self.hd, self.window,
                        value_dim=0 if self.vd == self.hd else self.vd) if self.own_kv else None
         if self.conv is None or self.taps == 1:
@@ -353,16 +400,21 @@ class Attention(Part):
                              "encoding or none")
         proj = linear_few(x, self.w_qkv, out_dtype=torch.float32) if proj is None else proj
         q = torch.empty((ctx.T, self.q_dim), dtype=self.dtype, device=proj.device)
+        if kv is None:
+            raise ValueError("attention: this layer reads another entry's keys and values, but "
+                             "the schedule gives it none")
+        own = self.own_kv
         ops.headnorm_rope_kv_append(
             proj, self.in_bias, self.q_head_w, self.k_head_w,
             float(self.head_norm["eps"]) if self.head_norm else 0.0, cos, sin, pairing, rot_dim,
-            ctx.tok_pos, ctx.tok_seq, ctx.seq_slot, self.nh, self.nkv, self.hd, self.vd, q,
-            table=kv.table, kc=kv.k, vc=kv.v, block_tokens=kv.block_tokens,
-            write_cache=cache.writes, fault=ctx.fault)
+            ctx.tok_pos, ctx.tok_seq, ctx.seq_slot, self.nh, self.nkv if own else 0, self.hd,
+            self.vd, q, table=kv.table, kc=kv.k, vc=kv.v, block_tokens=kv.block_tokens,
+            write_cache=cache.writes and own, fault=ctx.fault)
         o = torch.empty((ctx.T, self.o_dim), dtype=self.dtype, device=proj.device)
         self.attend(q, o, ctx, kv)
         if self.head_gate:
-            ops.gate_heads(o, proj[:, self.q_dim + self.kv_dim + self.v_dim:], self.nh, self.vd)
+            ops.gate_heads(o, proj[:, self.q_dim + (self.kv_dim + self.v_dim if own else 0):],
+                           self.nh, self.vd)
         if into is not None:
             linear_scaled_add(o, self.w_o, into, alpha)
             return None
@@ -479,9 +531,9 @@ class Attention(Part):
         return True
 
     def attend(self, q, o, ctx, kv):
-        run_attention(q, o, ctx, kv, self.nh, self.nkv, self.hd, self.scale, self.window,
+        run_attention(q, o, ctx, kv, self.nh, self.nkv, self.hd, self.scale, self.mask,
                       self.dtype, self.sink, vd=self.vd, bias=self.bias,
-                      bias_edges=self.bias_edges, bias_dense=self.bias_dense)
+                      bias_edges=self.bias_edges, bias_dense=self.bias_dense, slope=self.slope)
 
     def weight_bytes(self):
         return (self.w_qkv.numel() + self.w_o.numel()) * self.w_qkv.element_size()

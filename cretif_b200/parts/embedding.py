@@ -21,7 +21,9 @@ from .linear import linear
 class TokenEmbedding(Part):
     """params: ``name``; sized by the model's vocabulary (``vocab_size`` is injected).
     Optional ``positions`` (``{"name", "rows"}``): a learned vector per position, a table of
-    ``rows`` positions, added to the token's row as it is (32-bit sum)."""
+    ``rows`` positions, added to the token's row as it is (32-bit sum).  Optional ``norm``
+    (``{"name", "eps", "offset"}``): an RMS norm of the gathered row, its weight stored as the
+    factor minus ``offset``, in 32-bit, before the first layer reads the stream."""
 
     graph_safe = True
 
@@ -31,11 +33,21 @@ class TokenEmbedding(Part):
         pos = params.get("positions")
         if pos:
             out["positions"] = (pos["name"], WeightSpec((int(pos["rows"]), hidden_size)))
+        norm = params.get("norm")
+        if norm:
+            mean = 1.0 - float(norm.get("offset", 0.0))
+            out["norm"] = (norm["name"], WeightSpec((hidden_size,), init=(mean, 0.02)))
         return out
 
     def load(self, tensors):
         self.table = self._matrix(tensors["table"])
         self.positions = self._matrix(tensors["positions"]) if "positions" in tensors else None
+        self.norm_weight = None
+        if "norm" in tensors:
+            spec = self.params["norm"]
+            self.norm_weight = (self._vector32(tensors["norm"])
+                                + float(spec.get("offset", 0.0))).contiguous()
+            self.norm_eps = float(spec["eps"])
 
     def prepare(self, max_positions: int) -> None:
         if self.positions is not None and max_positions > self.positions.shape[0]:
@@ -46,11 +58,14 @@ class TokenEmbedding(Part):
         h = torch.empty((ids.numel(), self.hidden_size), dtype=torch.float32, device=ids.device)
         ops.embed_rows(self.table, ids, h, ctx.fault, positions=self.positions,
                        tok_pos=ctx.tok_pos if self.positions is not None else None)
+        if self.norm_weight is not None:
+            ops.rmsnorm_rows(h, self.norm_weight, self.norm_eps)
         return h
 
     def weight_bytes(self):
         n = self.table.numel() + (self.positions.numel() if self.positions is not None else 0)
-        return n * self.table.element_size()
+        return n * self.table.element_size() + (4 * self.hidden_size
+                                                if self.norm_weight is not None else 0)
 
 
 @register_part("head", "linear_head")
