@@ -21,7 +21,7 @@ fraction for each); ``prefill_b8`` and ``prefill_b64`` are steps over 8 and 64 p
 ``--dtype float32`` measures the true 32-bit path.
 Every weight plus the cache exceed the L2 cache, so no flush is needed between steps.
 
-    python bench.py --design rigozen|losorax|virorax [--design-size s|m] [--layers L]
+    python bench.py --design rigozen|losorax|virorax|mipurax [--design-size s|m] [--layers L]
 
 measures another thing and leaves the line above as it is: prefill (1 and 8 prompts of 2,048
 tokens) and decode (batch 1, 8, 64 from a context of 2,048) of Rigozen models whose layers
@@ -34,7 +34,10 @@ attention layer reads its neighbour's keys and values) beside Llama without a wi
 beside Rigozen's delta-rule layers.  ``--design virorax`` does it for Virorax models (all layers
 attention with biases, head norms, a sink and a gate; all layers retention; a mixture whose
 second half runs twice) beside Llama with the same window and beside Rigozen's delta-rule
-layers.
+layers.  ``--design mipurax`` does it for Mipurax models (all layers chunked attention with a
+slope by distance; all layers latent attention of either kind; dense and routed feed-forwards;
+a mixture in which every fourth layer reads an earlier layer's keys and values) beside Llama
+with a window as long as the chunk, Rigozen's latent attention and Losorax's routed experts.
 """
 from __future__ import annotations
 
@@ -401,6 +404,49 @@ def virorax_configs(z, layers):
     }
 
 
+def mipurax_configs(z, layers):
+    """name -> config.json of the models --design mipurax measures.  The latent plus the rotated
+    key part are as wide as Rigozen's latent (the attention kernels see one head of that size);
+    the chunk is as long as the other models' window; an expert has two matrices, so the routed
+    feed-forward's active width (top x expert_ff plus the shared expert) is again about half the
+    dense one's."""
+    rot = 32
+    lat = {"heads": z["heads"], "dim": z["dim"], "rot_dim": rot, "vdim": z["dim"],
+           "kv_rank": z["rank"] - rot, "q_rank": 3 * z["width"] // 8,
+           "scale": (z["dim"] + rot) ** -0.5, "rot": {"base": 500000.0, "dims": rot}}
+    att = {"heads": z["heads"], "kv_heads": z["kv"], "dim": z["dim"], "vdim": z["dim"],
+           "scale": z["dim"] ** -0.5, "mask": {"size": z["window"]}}
+    dense = {"kind": "dense", "ff": z["ff"]}
+    moe = {"kind": "moe", "expert": {"ff": z["expert_ff"]},
+           "router": {"experts": z["experts"], "top": z["top"],
+                      "groups": {"count": z["experts"] // 4, "keep": z["experts"] // 8}},
+           "shared": {"ff": z["expert_ff"]}}
+    kinds = {"attention": att, "latent_attention": lat, "latent_attention_2": lat}
+
+    def mipurax(order, mlp):
+        out = []
+        for i, k in enumerate(order):
+            if k == "attention_reader":
+                out.append({"type": "attention", "mixer": dict(att, kv_from=i - 2), "mlp": mlp})
+            else:
+                out.append({"type": k, "mixer": kinds[k], "mlp": mlp})
+        return {"architecture": "Mipurax", "vocab": z["vocab"], "width": z["width"],
+                "norm": {"eps": 1e-6}, "max_positions": CONTEXT, "layers": out}
+    mixed = (["latent_attention", "attention", "latent_attention_2", "attention_reader"]
+             * layers)[:layers]
+    base, los = design_configs(z, layers), losorax_configs(z, layers)
+    return {
+        "llama": base["llama"],
+        "rigozen latent_attention": base["rigozen latent_attention"],
+        "losorax attention routed": los["losorax attention routed"],
+        "mipurax attention dense": mipurax(["attention"] * layers, dense),
+        "mipurax attention routed": mipurax(["attention"] * layers, moe),
+        "mipurax latent dense": mipurax(["latent_attention"] * layers, dense),
+        "mipurax latent 2 dense": mipurax(["latent_attention_2"] * layers, dense),
+        "mipurax mixed routed": mipurax(mixed, moe),
+    }
+
+
 def design_configs(z, layers):
     """name -> config.json of the models --design measures."""
     att = {"heads": z["heads"], "kv_heads": z["kv"], "dim": z["dim"], "vdim": z["dim"],
@@ -449,6 +495,7 @@ def design_bench(args) -> int:
     rows = {}
     configs = (losorax_configs(z, layers) if args.design == "losorax"
                else virorax_configs(z, layers) if args.design == "virorax"
+               else mipurax_configs(z, layers) if args.design == "mipurax"
                else design_configs(z, layers))
     with ClockSampler() as clocks:
         for name, cfg in configs.items():
@@ -479,15 +526,19 @@ def design_bench(args) -> int:
             # routed experts: a token multiplies by `top` of them, a step reads those it uses
             routed = [l["mlp"] for l in cfg.get("layers", [])
                       if (l.get("mlp") or {}).get("kind") == "moe"]
-            expert_params = sum(3 * W * m["expert"]["ff"] * m["router"]["experts"] for m in routed)
+            # (an expert is three matrices with a gate, two without)
+            mats = 2 if cfg.get("architecture") == "Mipurax" else 3
+            expert_params = sum(mats * W * m["expert"]["ff"] * m["router"]["experts"]
+                                for m in routed)
             active_params = params - expert_params + sum(
-                3 * W * m["expert"]["ff"] * m["router"]["top"] for m in routed)
+                mats * W * m["expert"]["ff"] * m["router"]["top"] for m in routed)
             if params_run is not None:
                 active_params = params_run
 
             def read_params(b):
                 return params - expert_params + sum(
-                    3 * W * m["expert"]["ff"] * min(m["router"]["experts"], b * m["router"]["top"])
+                    mats * W * m["expert"]["ff"] * min(m["router"]["experts"],
+                                                       b * m["router"]["top"])
                     for m in routed)
             # the embedding table is read a row at a time; an output matrix of its own is
             # multiplied on the last rows only
@@ -495,7 +546,18 @@ def design_bench(args) -> int:
             tables = V * W * (2 if untied else 1)
             attn_flops = kept = 0.0
             for i, k in enumerate(kinds):
-                if k == "general_delta":
+                if cfg.get("architecture") == "Mipurax":
+                    m = cfg["layers"][i]["mixer"]
+                    if k == "attention":        # the keys of a query's own chunk; a reader keeps none
+                        chunk = m["mask"]["size"]
+                        keys = sum(p % chunk + 1 for p in range(T))
+                        attn_flops += 4.0 * keys * m["heads"] * m["dim"]
+                        kept += 2 * (2 * m["kv_heads"] * m["dim"]) * (T % chunk + 1)
+                    else:                       # every earlier key, latent plus rotated part
+                        wide = m["kv_rank"] + m["rot_dim"]
+                        attn_flops += 4.0 * (T * (T + 1) // 2) * m["heads"] * wide
+                        kept += 2 * wide * T
+                elif k == "general_delta":
                     attn_flops += T * z["d_heads"] * 8 * z["d_dim"] * z["d_dim"]
                     kept += 2 * 4 * z["d_heads"] * z["d_dim"] * z["d_dim"]
                 elif k == "retention":          # two multiply-adds a state element and token
@@ -631,7 +693,8 @@ def main() -> int:
                     help="skip the per-kernel shares of the decode step")
     ap.add_argument("--unequal", action="store_true",
                     help="prompts of unequal lengths 256..2,048 instead of 2,048 each")
-    ap.add_argument("--design", default=None, choices=["rigozen", "losorax", "virorax"],
+    ap.add_argument("--design", default=None,
+                    choices=["rigozen", "losorax", "virorax", "mipurax"],
                     help="measure this design at real layer sizes beside Llama at the same "
                          "sizes instead of the headline (another JSON line)")
     ap.add_argument("--design-size", default="m", choices=sorted(DESIGN_SIZES))

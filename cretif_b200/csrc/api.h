@@ -284,7 +284,10 @@ int cretif_attn_decode_mma_sink(const void* q, int ldq, void* out, int ldo, cons
                                 int window, int bt, int B, int n_splits, float* part_o,
                                 float* part_ml, int* counters, const float* sink,
                                 unsigned int* fault, void* stream);
-// ... and with a bias by distance (see cretif_attn_prefill_tc_bias).
+// ... and with a bias by distance (see cretif_attn_prefill_tc_bias).  head_groups = G > 1: more
+// than eight query heads on a key/value head go as G groups in one launch: B counts (sequence,
+// group) items, rows of q, out, tok_pos and tok_seq are laid out by item, item b serves heads
+// (b % G) * nh .. of the G * nh heads whose sink and bias rows follow one another.
 int cretif_attn_decode_mma_bias(const void* q, int ldq, void* out, int ldo, const void* kc,
                                 const void* vc, long long n_blocks, const int* table,
                                 int table_stride, const int* tok_pos, const int* tok_seq,
@@ -292,7 +295,7 @@ int cretif_attn_decode_mma_bias(const void* q, int ldq, void* out, int ldo, cons
                                 int window, int bt, int B, int n_splits, float* part_o,
                                 float* part_ml, int* counters, const float* sink,
                                 const float* bias_near, const float* bias_far, int n_far,
-                                unsigned int* fault, void* stream);
+                                int head_groups, unsigned int* fault, void* stream);
 
 // Fused decode projections (see decode_fused.cu).  H is the float32 residual stream; when it
 // is given, x = bf16(rmsnorm(H[rows])) is computed in the kernel, else X (bfloat16) is read.

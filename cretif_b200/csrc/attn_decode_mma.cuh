@@ -94,10 +94,14 @@ __host__ __device__ constexpr size_t dm_mrg_floats() {
 
 // A bias by distance: near [heads, n_far] and far [heads] (float32, times log2 e) are added to
 // the scaled score of the key n positions back, near[h, n] for n < n_far, far[h] beyond.
+// head_groups = G > 1: the launch's items are (sequence, group of heads) pairs, item b serving
+// heads (b % G) * nh .. of a model with G * nh query heads on these key/value heads; the rows of
+// q, out, tok_pos and tok_seq are laid out by item, the sink's and the bias's rows by head.
 struct DistanceBias {
   const float* near_;
   const float* far_;
   int n_far;
+  int head_groups;
 };
 
 template <int HD16, bool CLUSTER = false>
@@ -109,8 +113,16 @@ __device__ __forceinline__ void attn_decode_mma_item(
     float* __restrict__ part_o, float* __restrict__ part_ml, __nv_bfloat16* __restrict__ out,
     int ldo, int* __restrict__ counters, unsigned int* __restrict__ fault, int split,
     int n_splits, int kvh, int b, uint32_t& it_base, unsigned long long* stamps = nullptr,
-    int n_stages = kDmStages, const float* __restrict__ sink = nullptr,
-    DistanceBias bias = DistanceBias{nullptr, nullptr, 0}) {
+    int n_stages = kDmStages, const float* sink = nullptr,
+    DistanceBias bias = DistanceBias{nullptr, nullptr, 0, 1}) {
+  if (bias.head_groups > 1) {           // this item's heads start at head0 of the model's
+    const int head0 = (b % bias.head_groups) * nh;
+    if (sink) sink += head0;
+    if (bias.near_) {
+      bias.near_ += (size_t)head0 * bias.n_far;
+      bias.far_ += head0;
+    }
+  }
   // sink (may be null): one number per query head; exp(sink) joins the denominator of that
   // head's softmax where the ranges are merged, with no key and no value.
   constexpr int hd = HD16 * 16;

@@ -43,32 +43,38 @@ latent_in_kernel(const TI* __restrict__ proj, int ldp, int q_rank, int rank, int
                  const int* __restrict__ seq_slot, T* __restrict__ cq_out, int ldq,
                  const int* __restrict__ table, int table_stride, T* __restrict__ kc, int bt,
                  int write_cache, unsigned int* __restrict__ fault) {
-  __shared__ float scratch[33];
+  __shared__ float sums[2][8];
   __shared__ float kr[kLatMaxRot];
   const int t = blockIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const TI* row = proj + (size_t)t * ldp;
+  const TI* crow = row + q_rank;
+  // the two sums of squares in one pass over the row and one meeting of the warps
+  float sq = 0.f, sc = 0.f;
+  for (int i = threadIdx.x; i < q_rank; i += blockDim.x) {
+    const float v = to_float(row[i]);
+    sq += v * v;
+  }
+  for (int i = threadIdx.x; i < rank; i += blockDim.x) {
+    const float v = to_float(crow[i]);
+    sc += v * v;
+  }
+  for (int i = threadIdx.x; i < rot; i += blockDim.x) kr[i] = to_float(crow[rank + i]);
+  sq = warp_sum(sq);
+  sc = warp_sum(sc);
+  if (lane == 0) { sums[0][warp] = sq; sums[1][warp] = sc; }
+  __syncthreads();                              // (also publishes kr)
+  sq = sc = 0.f;
+#pragma unroll
+  for (int w = 0; w < 8; ++w) { sq += sums[0][w]; sc += sums[1][w]; }
   if (q_rank > 0) {
-    float ss = 0.f;
-    for (int i = threadIdx.x; i < q_rank; i += blockDim.x) {
-      const float v = to_float(row[i]);
-      ss += v * v;
-    }
-    ss = block_sum(ss, scratch);
-    const float inv = 1.0f / sqrtf(ss / (float)q_rank + eps);
+    const float inv = 1.0f / sqrtf(sq / (float)q_rank + eps);
     T* dst = cq_out + (size_t)t * ldq;
     for (int i = threadIdx.x; i < q_rank; i += blockDim.x)
       dst[i] = from_float<T>(to_float(row[i]) * inv * wq[i]);
   }
   if (!write_cache) return;
-  const TI* crow = row + q_rank;
-  float ss = 0.f;
-  for (int i = threadIdx.x; i < rank; i += blockDim.x) {
-    const float v = to_float(crow[i]);
-    ss += v * v;
-  }
-  for (int i = threadIdx.x; i < rot; i += blockDim.x) kr[i] = to_float(crow[rank + i]);
-  ss = block_sum(ss, scratch);                  // (its barriers also publish kr)
-  const float inv = 1.0f / sqrtf(ss / (float)rank + eps);
+  const float inv = 1.0f / sqrtf(sc / (float)rank + eps);
   const int pos = tok_pos[t];
   const int slot = seq_slot[tok_seq[t]];
   const int blk = table[(size_t)slot * table_stride + pos / bt];
@@ -106,6 +112,19 @@ rope_heads_kernel(const TI* __restrict__ q, int ldq, int nh, int d, int rot,
   const float* s = sin_t + (size_t)pos * (rot >> 1);
   T* dst = out + (size_t)t * ldo + (size_t)h * ldh + off;
   for (int i = lane; i < rot; i += 32) dst[i] = from_float<T>(rotated(mine, i, rot, pairing, c, s));
+}
+
+// a CTA per row, for a few rows: a lone warp would wait for its loads one after the other
+__global__ void __launch_bounds__(256)
+rmsnorm_row_block_kernel(float* __restrict__ x, int ld, const float* __restrict__ w, int H,
+                         float eps) {
+  __shared__ float scratch[33];
+  float* row = x + (size_t)blockIdx.x * ld;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) ss += row[i] * row[i];
+  ss = block_sum(ss, scratch);
+  const float inv = 1.0f / sqrtf(ss / (float)H + eps);
+  for (int i = threadIdx.x; i < H; i += blockDim.x) row[i] = row[i] * inv * w[i];
 }
 
 // a warp per row
@@ -182,7 +201,10 @@ extern "C" int cretif_rmsnorm_rows(float* x, int ld, const float* w, int R, int 
                                    void* stream) {
   if (R <= 0) return kOk;
   if (H <= 0 || ld < H || !w) return kBadArgument;
-  rmsnorm_rows_kernel<<<(unsigned)((R + 7) / 8), 256, 0, (cudaStream_t)stream>>>(x, ld, w, R, H,
-                                                                                 eps);
+  if (R <= 64)
+    rmsnorm_row_block_kernel<<<R, 256, 0, (cudaStream_t)stream>>>(x, ld, w, H, eps);
+  else
+    rmsnorm_rows_kernel<<<(unsigned)((R + 7) / 8), 256, 0, (cudaStream_t)stream>>>(x, ld, w, R, H,
+                                                                                   eps);
   return launch_status();
 }

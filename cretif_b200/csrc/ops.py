@@ -1163,22 +1163,30 @@ def decode_plan(B: int, nkv: int, max_context: int, device, hd: int = 64):
 
 def attn_decode(q, out, kc, vc, table, tok_pos, tok_seq, seq_slot, nh: int, nkv: int, hd: int,
                 scale: float, window: int, block_tokens: int, n_splits: int, fault,
-                cluster: bool = False, sink=None, bias_near=None, bias_far=None) -> None:
-    """``sink`` (float32 [heads], optional; tensor-core kernel only): exp(sink_h) joins head h's
+                cluster: bool = False, sink=None, bias_near=None, bias_far=None,
+                head_groups: int = 1) -> None:
+    """``head_groups`` = G > 1 (tensor-core kernel only): more than eight query heads on a
+    key/value head in ONE launch; the rows of ``q``, ``out``, ``tok_pos`` and ``tok_seq`` are
+    (sequence, group of ``nh`` heads) items, G of them a sequence, while ``sink`` and the bias
+    keep a row per head of all G·nh.  ``sink`` (float32 [heads], optional; tensor-core kernel only): exp(sink_h) joins head h's
     softmax denominator.  ``bias_near`` [heads, n_far] with ``bias_far`` [heads] (float32, times
     log2 e; tensor-core kernel only): what the key n positions back adds to its scaled score."""
     n_far = 0
     if bias_near is not None:
         _need(bias_near, "bias_near", torch.float32, 2); _need(bias_far, "bias_far", torch.float32, 1)
         n_far = bias_near.shape[1]
-        if (bias_near.shape[0] != nh or bias_far.numel() != nh or not bias_near.is_contiguous()
+        if (bias_near.shape[0] != nh * head_groups or bias_far.numel() != nh * head_groups
+                or not bias_near.is_contiguous()
                 or not bias_far.is_contiguous() or hd > 128 or _decode_simt_only):
             raise KernelError("attn_decode: the bias is [heads, distances] with one far value "
                               "per head, and needs head_dim <= 128")
     if sink is not None:
         _need(sink, "sink", torch.float32, 1)
-        if sink.numel() != nh or hd > 128 or _decode_simt_only:
+        if sink.numel() != nh * head_groups or hd > 128 or _decode_simt_only:
             raise KernelError("attn_decode: a sink needs one number per head and head_dim <= 128")
+    if head_groups > 1 and (hd > 128 or _decode_simt_only or q.shape[0] % head_groups):
+        raise KernelError("attn_decode: groups of heads need head_dim <= 128 and whole "
+                          "sequences of items")
     _need(q, "q", torch.bfloat16, 2); _need(out, "out", torch.bfloat16, 2)
     _need(kc, "k cache", torch.bfloat16, 4); _need(vc, "v cache", torch.bfloat16, 4)
     B = q.shape[0]
@@ -1195,7 +1203,8 @@ def attn_decode(q, out, kc, vc, table, tok_pos, tok_seq, seq_slot, nh: int, nkv:
             _p(q), _rows(q, "q"), _p(out), _rows(out, "out"), _p(kc), _p(vc),
             ctypes.c_longlong(kc.shape[0]), _p(table), table.stride(0), _p(tok_pos), _p(tok_seq),
             _p(seq_slot), nh, nkv, hd, ctypes.c_float(scale), window, block_tokens, B, n_splits,
-            None, None, None, _p(sink), _p(bias_near), _p(bias_far), n_far, _p(fault), _stream()),
+            None, None, None, _p(sink), _p(bias_near), _p(bias_far), n_far, head_groups, _p(fault),
+            _stream()),
             "attn_decode_mma")
         return
     part_o = torch.empty((B, nh, n_splits, hd), dtype=torch.float32, device=q.device)
@@ -1207,7 +1216,7 @@ def attn_decode(q, out, kc, vc, table, tok_pos, tok_seq, seq_slot, nh: int, nkv:
             ctypes.c_longlong(kc.shape[0]), _p(table), table.stride(0), _p(tok_pos), _p(tok_seq),
             _p(seq_slot), nh, nkv, hd, ctypes.c_float(scale), window, block_tokens, B, n_splits,
             _p(part_o), _p(part_ml), _p(counters), _p(sink), _p(bias_near), _p(bias_far), n_far,
-            _p(fault), _stream()), "attn_decode_mma")
+            head_groups, _p(fault), _stream()), "attn_decode_mma")
         return
     _check(lib().cretif_attn_decode(
         _p(q), _rows(q, "q"), _p(out), _rows(out, "out"), _p(kc), _p(vc), _p(table),

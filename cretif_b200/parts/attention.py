@@ -123,7 +123,24 @@ def run_attention(q, o, ctx, kv, nh, nkv, hd, scale, window, dtype, sink=None, v
         if ctx.is_decode and ops.attn_decode_supported(hd, kv.block_tokens, min(nh // nkv, 8)) \
                 and (nh // nkv <= 8 or nkv == 1):
             # the kernel takes up to eight query heads per key/value head; more heads on ONE
-            # key/value head (a shared latent) go eight at a time
+            # key/value head (a shared latent) go as groups of eight in one launch whose items
+            # are (sequence, group) pairs, where the rows allow that view ...
+            G = nh // 8
+            if (nh // nkv > 8 and nh % 8 == 0 and hd <= 128 and q.stride(0) == nh * hd
+                    and o.stride(0) == nh * hd and ops.attn_decode_supported(hd, kv.block_tokens, 8)):
+                key = ("decode_head_groups", G)
+                if key not in ctx.extras:       # once a step, for every layer that asks
+                    # (materialised: a stride-0 view of one sequence's entry is no array)
+                    ctx.extras[key] = tuple(t.repeat_interleave(G).contiguous()
+                                            for t in (ctx.tok_pos, ctx.tok_seq))
+                pos_g, seq_g = ctx.extras[key]
+                splits, cluster = ops.decode_plan(ctx.B * G, 1, ctx.max_context, q.device, hd)
+                ops.attn_decode(q.view(ctx.B * G, 8 * hd), o.view(ctx.B * G, 8 * hd), kv.k, kv.v,
+                                kv.table, pos_g, seq_g, ctx.seq_slot, 8, 1, hd, scale, window,
+                                kv.block_tokens, splits, ctx.fault, cluster, sink=sink,
+                                bias_near=near, bias_far=far, head_groups=G)
+                return
+            # ... else eight at a time
             step = nh if nh // nkv <= 8 else 8
             for h0 in range(0, nh, step):
                 n = min(step, nh - h0)

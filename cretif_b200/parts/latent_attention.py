@@ -134,28 +134,31 @@ class LatentAttention(Part):
     def cache_request(self):
         return KVRequest(1, self.key_dim, self.window, shared_values=True)
 
-    def _forward_extended(self, x, ctx, cache, into=None):
-        """The queries through their latent, a rotated part beside the latent, an output gate."""
+    def _forward_extended(self, x, ctx, cache, into=None, proj=None):
+        """The queries through their latent, a rotated part beside the latent, an output gate.
+        ``proj``: the input product's 32-bit result, where the caller made it already."""
         H, d, e, r, rot, T, D = self.nh, self.hd, self.vd, self.rank, self.rot, ctx.T, self.key_dim
         kv = cache.kv
         cos = sin = None
         pairing = 0
         if self.position is not None:
             cos, sin, pairing, _ = self.position.rotary_table()
-        proj = linear(x, self.w_in, out_dtype=torch.float32)        # [cq | c | kr | gates | 0]
-        cq = torch.empty((T, self.q_rank), dtype=self.dtype, device=x.device)
+        if proj is None:
+            proj = linear(x, self.w_in, out_dtype=torch.float32)    # [cq | c | kr | gates | 0]
+        dev = proj.device
+        cq = torch.empty((T, self.q_rank), dtype=self.dtype, device=dev)
         ops.latent_in(proj, self.q_rank, r, rot, self.q_norm, self.down_norm, self.eps, cos, sin,
                       pairing, ctx.tok_pos, ctx.tok_seq, ctx.seq_slot, cq, table=kv.table,
                       kc=kv.k, block_tokens=kv.block_tokens, write_cache=cache.writes,
                       fault=ctx.fault)
         q = linear(cq, self.w_q_up)                                   # [T, H (d + rot)]
-        q_lat = torch.empty((T, H, D), dtype=self.dtype, device=x.device)
+        q_lat = torch.empty((T, H, D), dtype=self.dtype, device=dev)
         ops.gemm_batched(q.view(T, H, d + rot)[:, :, :d], self.w_q_latent, q_lat[:, :, :r])
         ops.rope_heads(q, H, d, rot, cos, sin, pairing, ctx.tok_pos, q_lat, r)
-        o_lat = torch.empty((T, H * D), dtype=self.dtype, device=x.device)
+        o_lat = torch.empty((T, H * D), dtype=self.dtype, device=dev)
         run_attention(q_lat.view(T, H * D), o_lat, ctx, kv, H, 1, D, self.scale, self.window,
                       self.dtype, self.sink)
-        o = torch.empty((T, H, e), dtype=self.dtype, device=x.device)
+        o = torch.empty((T, H, e), dtype=self.dtype, device=dev)
         ops.gemm_batched(o_lat.view(T, H, D)[:, :, :r], self.w_up_v, o)
         o = o.view(T, H * e)
         if self.gate:
@@ -194,9 +197,16 @@ class LatentAttention(Part):
         return linear(o.view(T, H * e), self.w_o, out_dtype=torch.float32)
 
     def forward_from_residual(self, h, norm, ctx, cache) -> bool:
-        """The block's norm by its own kernel, the output product added into ``h``."""
+        """The output product is added into ``h``.  Few tokens in bfloat16: the block's norm runs
+        in the prologue of the input product; else the norm has a kernel of its own."""
         if norm is None or h.dtype != torch.float32 or not h.is_contiguous():
             return False
+        if self.extended and self.dtype == torch.bfloat16:
+            from .linear import normed_linear_few
+            proj = normed_linear_few(h, norm, self.w_in, torch.float32)
+            if proj is not None:
+                self._forward_extended(None, ctx, cache, into=h, proj=proj)
+                return True
         self.forward(norm.forward(h, None), ctx, cache, into=h)
         return True
 

@@ -387,6 +387,33 @@ def test_whole_and_token_by_token(engines, plain_logits, name, dtype):
     eng.cache.check()
 
 
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_few_token_steps_with_and_without_the_fused_kernels(folders, plain_logits, name):
+    """bfloat16 steps of a few tokens norm the rows inside the mixers' input products and apply
+    the feed-forward's activation in the products' epilogues; with the few-token kernels switched
+    off the same steps take the separate kernels.  Both ways give the plain implementation's
+    logits, and each other's up to the order of summation."""
+    from cretif_b200.csrc import ops
+    from cretif_b200.engine import Engine
+    from cretif_b200.parts.attention import enable_fused_steps
+    eng = Engine(folders[name], dtype="bfloat16", max_tokens=512, step_graphs=False)
+    toks = tiny.tokens(name, 40, 7)
+    want = plain_logits(name, toks)
+    got = {}
+    try:
+        for on in (True, False):
+            enable_fused_steps(on)
+            before = ops.launch_count()
+            got[on] = run_chunks(eng, toks, [3, 1, 1, 5, 2, 1, 27])
+            launches = ops.launch_count() - before
+            assert close(got[on], want, "bfloat16"), (name, on)
+            got[on] = (got[on], launches)
+    finally:
+        enable_fused_steps(True)
+    assert got[True][1] < got[False][1]                 # fewer kernels the fused way
+    assert rel_err(got[True][0], got[False][0]) < 3e-2
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_portions_of_a_prompt(engines, plain_logits, name, dtype):
