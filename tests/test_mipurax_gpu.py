@@ -310,6 +310,61 @@ def test_attention_kernels_with_chunks_and_a_slope(H, G, d, chunk):
     assert int(fault.item()) == 0
 
 
+@pytest.mark.parametrize("H,d,B", [(16, 96, 1), (32, 128, 3), (24, 64, 2), (12, 48, 2)])
+def test_many_heads_on_one_key_value_head_decode(H, d, B):
+    """Single tokens of B sequences of unequal length over one shared key/value head whose
+    values are its keys (a cached latent), with a sink per head: groups of eight heads go in one
+    launch where the head count allows, else eight at a time; both against the plain softmax."""
+    from cretif_b200.csrc import ops
+    from cretif_b200.parts.attention import run_attention
+    from cretif_b200.parts.base import StepContext
+    g = torch.Generator().manual_seed(H + d)
+    lens = [150, 77, 201][:B]
+    dev = torch.device("cuda")
+    i32 = dict(dtype=torch.int32, device=dev)
+    n_blocks = sum((n + 63) // 64 for n in lens) + 1
+    kc = torch.zeros(n_blocks, 1, 64, d, dtype=torch.bfloat16, device=dev)
+    table = torch.full((B, 8), -1, **i32)
+    ks, at = [], 0
+    for b, n in enumerate(lens):
+        k = torch.randn(n, d, generator=g).bfloat16()
+        ks.append(k)
+        for p in range(n):
+            if p % 64 == 0:
+                table[b, p // 64] = n_blocks - 1 - at
+                at += 1
+            kc[int(table[b, p // 64]), 0, p % 64] = k[p].cuda()
+    q = (torch.randn(B, H, d, generator=g) * 1.5).bfloat16()
+    sink = torch.randn(H, generator=g) * 2
+    scale = 0.8 / d ** 0.5
+    want = torch.zeros(B, H, d, dtype=torch.float64)
+    for b, n in enumerate(lens):
+        s = torch.einsum("hd,jd->hj", q[b].double(), ks[b].double()) * scale
+        w = plain.softmax_rows(s[:, None, :], torch.ones(1, n, dtype=torch.bool), sink.double())
+        want[b] = w[:, 0] @ ks[b].double()
+
+    class KV:
+        pass
+    kv = KV()
+    kv.k, kv.v, kv.table, kv.block_tokens, kv.window = kc, kc, table, 64, 0
+    fault = torch.zeros(1, **i32)
+    ctx = StepContext(T=B, B=B, tok_ids=torch.zeros(B, **i32),
+                      tok_pos=torch.tensor([n - 1 for n in lens], **i32),
+                      tok_seq=torch.arange(B, **i32), seq_slot=torch.arange(B, **i32),
+                      seq_start=torch.tensor([n - 1 for n in lens], **i32),
+                      cu_seqlens=torch.arange(B + 1, **i32), is_decode=True, max_new=1,
+                      max_context=512, fault=fault, dtype=torch.bfloat16, device=dev)
+    out = torch.zeros(B, H * d, dtype=torch.bfloat16, device=dev)
+    before = ops.launch_count()
+    run_attention(q.reshape(B, H * d).cuda(), out, ctx, kv, H, 1, d, scale, 0, torch.bfloat16,
+                  sink.cuda())
+    launches = ops.launch_count() - before
+    assert launches == (1 if H % 8 == 0 else -(-H // 8)), launches
+    err = (out.cpu().double() - want.reshape(B, H * d)).abs().max()
+    assert err <= 2e-2 * want.abs().max(), float(err)
+    assert int(fault.item()) == 0
+
+
 # ------------------------------------------------------------------ each mechanism alone in a model
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("kind", ["attention", "latent_attention", "latent_attention_2"])
