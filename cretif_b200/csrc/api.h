@@ -295,7 +295,8 @@ int cretif_attn_decode_mma_bias(const void* q, int ldq, void* out, int ldo, cons
                                 int window, int bt, int B, int n_splits, float* part_o,
                                 float* part_ml, int* counters, const float* sink,
                                 const float* bias_near, const float* bias_far, int n_far,
-                                int head_groups, unsigned int* fault, void* stream);
+                                int head_groups, const float* bias_slope, unsigned int* fault,
+                                void* stream);
 
 // Fused decode projections (see decode_fused.cu).  H is the float32 residual stream; when it
 // is given, x = bf16(rmsnorm(H[rows])) is computed in the kernel, else X (bfloat16) is read.
@@ -349,14 +350,17 @@ int cretif_attn_prefill_tc_sink(const void* qkv, int ldq, int T, void* out, int 
                                 const float* sink, unsigned int* fault, void* stream);
 // ... and with a bias by distance: bias_near [nh, n_far] and bias_far [nh] (float32, already
 // multiplied by log2 e; both null for none) are added to the scaled score of the key n positions
-// back, bias_near[h, n] for n < n_far and bias_far[h] for every n beyond.
+// back, bias_near[h, n] for n < n_far and bias_far[h] for every n beyond.  bias_slope [nh]
+// (float32, times log2 e; null for none, not together with the table): n times bias_slope[h] is
+// taken off that score instead, at any distance.
 int cretif_attn_prefill_tc_bias(const void* qkv, int ldq, int T, void* out, int ldo,
                                 const void* kc, const void* vc, long long n_blocks,
                                 const int* table, int table_stride, const int* cu_seqlens,
                                 const int* seq_start, const int* seq_slot, int nh, int nkv, int hd,
                                 float scale, int window, int bt, int B, int max_new,
                                 const float* sink, const float* bias_near, const float* bias_far,
-                                int n_far, unsigned int* fault, void* stream);
+                                int n_far, const float* bias_slope, unsigned int* fault,
+                                void* stream);
 
 // Per-head work of an attention whose projections are normed head by head (head_ops.cu).
 // proj rows [q (nh hd) | k (nkv hd) | v (nkv vd) | ...] (float32 or bfloat16): + bias (null for

@@ -106,7 +106,7 @@ extern "C" int cretif_attn_decode_mma_sink(const void* q, int ldq, void* out, in
   return cretif_attn_decode_mma_bias(q, ldq, out, ldo, kc, vc, n_blocks, table, table_stride,
                                      tok_pos, tok_seq, seq_slot, nh, nkv, hd, scale, window, bt, B,
                                      n_splits, part_o, part_ml, counters, sink, nullptr, nullptr,
-                                     0, 1, fault, stream);
+                                     0, 1, nullptr, fault, stream);
 }
 
 // bias_near [nh, n_far], bias_far [nh] (float32, times log2 e; both null for none): added to the
@@ -119,13 +119,13 @@ extern "C" int cretif_attn_decode_mma_bias(const void* q, int ldq, void* out, in
                                            int n_splits, float* part_o, float* part_ml,
                                            int* counters, const float* sink,
                                            const float* bias_near, const float* bias_far,
-                                           int n_far, int head_groups, unsigned int* fault,
-                                           void* stream) {
+                                           int n_far, int head_groups, const float* bias_slope,
+                                           unsigned int* fault, void* stream) {
   if (B <= 0) return kOk;
   if ((bias_near != nullptr) != (bias_far != nullptr) || (bias_near && n_far < 1) ||
-      head_groups < 1 || B % head_groups)
+      head_groups < 1 || B % head_groups || (bias_near && bias_slope))
     return kBadArgument;
-  const DistanceBias bias{bias_near, bias_far, n_far, head_groups};
+  const DistanceBias bias{bias_near, bias_far, n_far, head_groups, bias_slope};
   if (nh <= 0 || nkv <= 0 || nh % nkv || nh / nkv > 8 || hd % 16 || hd < 16 || hd > 128 ||
       bt != kDmTile || n_splits <= 0 || n_splits > kDmTile || nkv > 65535 || B > 65535 ||
       ldq % 2)

@@ -102,6 +102,7 @@ struct DistanceBias {
   const float* far_;
   int n_far;
   int head_groups;
+  const float* slope_;      // [heads], times log2 e: n times it is taken off instead of a table
 };
 
 template <int HD16, bool CLUSTER = false>
@@ -114,7 +115,7 @@ __device__ __forceinline__ void attn_decode_mma_item(
     int ldo, int* __restrict__ counters, unsigned int* __restrict__ fault, int split,
     int n_splits, int kvh, int b, uint32_t& it_base, unsigned long long* stamps = nullptr,
     int n_stages = kDmStages, const float* sink = nullptr,
-    DistanceBias bias = DistanceBias{nullptr, nullptr, 0, 1}) {
+    DistanceBias bias = DistanceBias{nullptr, nullptr, 0, 1, nullptr}) {
   if (bias.head_groups > 1) {           // this item's heads start at head0 of the model's
     const int head0 = (b % bias.head_groups) * nh;
     if (sink) sink += head0;
@@ -122,6 +123,7 @@ __device__ __forceinline__ void attn_decode_mma_item(
       bias.near_ += (size_t)head0 * bias.n_far;
       bias.far_ += head0;
     }
+    if (bias.slope_) bias.slope_ += head0;
   }
   // sink (may be null): one number per query head; exp(sink) joins the denominator of that
   // head's softmax where the ranges are merged, with no key and no value.
@@ -291,6 +293,8 @@ __device__ __forceinline__ void attn_decode_mma_item(
             const int head = kvh * g + r, dist = pos - key;
             sv += dist >= bias.n_far ? __ldg(bias.far_ + head)
                                      : __ldg(bias.near_ + (size_t)head * bias.n_far + dist);
+          } else if (bias.slope_ && valid && r < g) {
+            sv -= __ldg(bias.slope_ + kvh * g + r) * (float)(pos - key);
           }
           t4[n * 2 + e] = valid ? sv : -INFINITY;
         }

@@ -98,9 +98,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
                        int window, unsigned int* __restrict__ fault,
                        unsigned long long* stamps, const float* __restrict__ sink,
                        const float* __restrict__ bias_near, const float* __restrict__ bias_far,
-                       int n_far) {
+                       int n_far, const float* __restrict__ bias_slope) {
   // bias_near [nh, n_far], bias_far [nh] (both times log2 e, may be null): what is added to the
-  // scaled score of the key n positions back, for n < n_far and for every n beyond
+  // scaled score of the key n positions back, for n < n_far and for every n beyond.
+  // bias_slope [nh] (times log2 e, may be null; not together with the table): n times it is
+  // taken off that score instead, computed and not looked up
   extern __shared__ unsigned char smem_raw[];
   // Tuning aid: with a buffer given, the first CTA (the heaviest tile) notes the times at
   // which its MMA thread and one softmax thread pass the phases of steps 0 .. 7:
@@ -312,7 +314,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
       asm volatile("bar.sync 5, 256;" ::: "memory");
     }
     // with a bias the scores are scaled and biased first and the softmax then takes them as they are
-    const float sc_log2 = bias_near ? 1.0f : scale_log2;
+    const float sc_log2 = (bias_near || bias_slope) ? 1.0f : scale_log2;
+    const float slope_l2 = bias_slope ? bias_slope[h] : 0.f;
     for (int j = 0; j < n_tiles; ++j) {
       if (warp == 2) stamp(j, 0);
       unsigned char* prow = prow0 + (defer ? (j & 1) * kPBytes : 0);
@@ -354,6 +357,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
             t[c] = fmaf(t[c], scale_log2, bv);          // a masked score stays -inf
           }
         }
+      } else if (bias_slope) {
+        // slope * (key - query position): two multiply-adds a score, no table
+        const float base = slope_l2 * (float)(key0 - q_pos);
+#pragma unroll
+        for (int c = 0; c < 64; ++c) t[c] = fmaf(t[c], scale_log2, fmaf(slope_l2, (float)c, base));
       }
       // (three-input maxima and two-wide float operations halve the instructions of the
       // loops below: what bounds a step is how many instructions its eight warps can issue)
@@ -927,11 +935,14 @@ extern "C" int cretif_attn_prefill_tc_sink(const void* qkv, int ldq, int T, void
                                            void* stream) {
   return cretif_attn_prefill_tc_bias(qkv, ldq, T, out, ldo, kc, vc, n_blocks, table, table_stride,
                                      cu_seqlens, seq_start, seq_slot, nh, nkv, hd, scale, window,
-                                     bt, B, max_new, sink, nullptr, nullptr, 0, fault, stream);
+                                     bt, B, max_new, sink, nullptr, nullptr, 0, nullptr, fault,
+                                     stream);
 }
 
 // bias_near [nh, n_far] and bias_far [nh] (float32, times log2 e; both null for none): added to
 // the scaled score of the key n positions back, bias_near[h, n] for n < n_far, bias_far[h] beyond.
+// bias_slope [nh] (float32, times log2 e; null for none, not together with the table): n times
+// bias_slope[h] is taken off that score, at any distance.
 extern "C" int cretif_attn_prefill_tc_bias(const void* qkv, int ldq, int T, void* out, int ldo,
                                            const void* kc, const void* vc, long long n_blocks,
                                            const int* table, int table_stride,
@@ -939,10 +950,12 @@ extern "C" int cretif_attn_prefill_tc_bias(const void* qkv, int ldq, int T, void
                                            const int* seq_slot, int nh, int nkv, int hd,
                                            float scale, int window, int bt, int B, int max_new,
                                            const float* sink, const float* bias_near,
-                                           const float* bias_far, int n_far, unsigned int* fault,
+                                           const float* bias_far, int n_far,
+                                           const float* bias_slope, unsigned int* fault,
                                            void* stream) {
   if (B <= 0 || T <= 0) return kOk;
-  if ((bias_near != nullptr) != (bias_far != nullptr) || (bias_near && (n_far < 1 || n_far > 8192)))
+  if ((bias_near != nullptr) != (bias_far != nullptr) || (bias_near && (n_far < 1 || n_far > 8192)) ||
+      (bias_near && bias_slope))
     return kBadArgument;
   if (nh <= 0 || nkv <= 0 || nh % nkv || hd % 16 || hd < 16 || hd > 128 || bt != kPfBlk ||
       !(scale > 0.f) || max_new <= 0 || B > 65535 || ldq % 8 || ldo % 8 ||
@@ -987,7 +1000,7 @@ extern "C" int cretif_attn_prefill_tc_bias(const void* qkv, int ldq, int T, void
   }
   // (its two slots keep a bias table each: up to 2 x 4,096 distances beside the K/V stages)
   const bool rows_ok = g_pf_pairing != 0 && hd <= 64 && window == 0 && items <= 65535 &&
-                       (!bias_near || n_far <= 4096);
+                       (!bias_near || n_far <= 4096) && !bias_slope;
   const bool paired = rows_ok && (g_pf_pairing == 1 ||
                                   (g_pf_pairing < 0 && 5 * pairs * nkv * B >= 7LL * sm_count));
   if (rows_ok) {
@@ -1022,7 +1035,7 @@ extern "C" int cretif_attn_prefill_tc_bias(const void* qkv, int ldq, int T, void
     e = cudaLaunchKernelEx(&cfg, attn_prefill_tc_kernel<64>, map_q, map_k, map_v,
                            (__nv_bfloat16*)out, ldo, table, table_stride, cu_seqlens, seq_start,
                            seq_slot, nh, nkv, hd, scale_log2, window, fault, g_pf_stamps, sink,
-                           bias_near, bias_far, n_far);
+                           bias_near, bias_far, n_far, bias_slope);
     if (e != cudaSuccess) return (int)e;
   } else {
     static int configured = 0;
@@ -1035,7 +1048,7 @@ extern "C" int cretif_attn_prefill_tc_bias(const void* qkv, int ldq, int T, void
     e = cudaLaunchKernelEx(&cfg, attn_prefill_tc_kernel<128>, map_q, map_k, map_v,
                            (__nv_bfloat16*)out, ldo, table, table_stride, cu_seqlens, seq_start,
                            seq_slot, nh, nkv, hd, scale_log2, window, fault, g_pf_stamps, sink,
-                           bias_near, bias_far, n_far);
+                           bias_near, bias_far, n_far, bias_slope);
     if (e != cudaSuccess) return (int)e;
   }
   return launch_status();

@@ -91,6 +91,91 @@ latent_in_kernel(const TI* __restrict__ proj, int ldp, int q_rank, int rank, int
     dst[rank + i] = from_float<T>(rotated(kr, i, rot, pairing, c, s));
 }
 
+// The same for many tokens: a warp per token, no barrier; the second pass over the row finds it
+// in the cache.
+template <typename TI, typename T>
+__global__ void __launch_bounds__(256)
+latent_in_rows_kernel(const TI* __restrict__ proj, int ldp, int q_rank, int rank, int rot,
+                      const float* __restrict__ wq, const float* __restrict__ wc, float eps,
+                      const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                      int pairing, const int* __restrict__ tok_pos,
+                      const int* __restrict__ tok_seq, const int* __restrict__ seq_slot,
+                      T* __restrict__ cq_out, int ldq, const int* __restrict__ table,
+                      int table_stride, T* __restrict__ kc, int bt, int write_cache, int T_tokens,
+                      unsigned int* __restrict__ fault) {
+  const int lane = threadIdx.x & 31;
+  const int t = blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (t >= T_tokens) return;
+  const TI* row = proj + (size_t)t * ldp;
+  const TI* crow = row + q_rank;
+  float sq = 0.f, sc = 0.f;
+#pragma unroll 8
+  for (int i = lane; i < q_rank; i += 32) {
+    const float v = to_float(row[i]);
+    sq += v * v;
+  }
+#pragma unroll 4
+  for (int i = lane; i < rank; i += 32) {
+    const float v = to_float(crow[i]);
+    sc += v * v;
+  }
+  sq = warp_sum(sq);
+  sc = warp_sum(sc);
+  if (q_rank > 0) {
+    const float inv = 1.0f / sqrtf(sq / (float)q_rank + eps);
+    T* dst = cq_out + (size_t)t * ldq;
+#pragma unroll 8
+    for (int i = lane; i < q_rank; i += 32) dst[i] = from_float<T>(to_float(row[i]) * inv * wq[i]);
+  }
+  if (!write_cache) return;
+  const float inv = 1.0f / sqrtf(sc / (float)rank + eps);
+  const int pos = tok_pos[t];
+  const int slot = seq_slot[tok_seq[t]];
+  const int blk = table[(size_t)slot * table_stride + pos / bt];
+  if (blk < 0) {
+    if (lane == 0) atomicOr(fault, kFaultBlockTable);
+    return;
+  }
+  T* dst = kc + ((size_t)blk * bt + (pos % bt)) * (rank + rot);
+#pragma unroll 4
+  for (int i = lane; i < rank; i += 32) dst[i] = from_float<T>(to_float(crow[i]) * inv * wc[i]);
+  const int half = rot >> 1;
+  const float* c = cos_t + (size_t)pos * half;
+  const float* s = sin_t + (size_t)pos * half;
+  const TI* kr = crow + rank;
+  for (int i = lane; i < rot; i += 32) {
+    const bool first = pairing ? !(i & 1) : i < half;
+    const int j = pairing ? i >> 1 : (first ? i : i - half);
+    const int partner = pairing ? i ^ 1 : (first ? i + half : i - half);
+    const float u = to_float(kr[i]), v = to_float(kr[partner]);
+    dst[rank + i] = from_float<T>(first ? u * c[j] - v * s[j] : u * c[j] + v * s[j]);
+  }
+}
+
+// many tokens: a thread per (token, head, pair of channels)
+template <typename TI, typename T>
+__global__ void __launch_bounds__(256)
+rope_pairs_kernel(const TI* __restrict__ q, int ldq, int nh, int d, int rot,
+                  const float* __restrict__ cos_t, const float* __restrict__ sin_t, int pairing,
+                  const int* __restrict__ tok_pos, T* __restrict__ out, int ldo, int ldh, int off,
+                  long long total) {
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= total) return;
+  const int half = rot >> 1;
+  const int j = (int)(idx % half);
+  const long long th = idx / half;
+  const int h = (int)(th % nh);
+  const long long t = th / nh;
+  const int a = pairing ? 2 * j : j, b = pairing ? 2 * j + 1 : j + half;
+  const TI* src = q + (size_t)t * ldq + (size_t)h * (d + rot) + d;
+  const float u = to_float(src[a]), v = to_float(src[b]);
+  const int pos = tok_pos[t];
+  const float c = cos_t[(size_t)pos * half + j], s = sin_t[(size_t)pos * half + j];
+  T* dst = out + (size_t)t * ldo + (size_t)h * ldh + off;
+  dst[a] = from_float<T>(u * c - v * s);
+  dst[b] = from_float<T>(v * c + u * s);
+}
+
 // a warp per (token, head)
 template <typename TI, typename T>
 __global__ void __launch_bounds__(256)
@@ -162,10 +247,21 @@ extern "C" int cretif_latent_in(const void* proj, int ldp, int proj_dt, int q_ra
     return kBadArgument;
   if (write_cache && (bt <= 0 || !kc || !table || !tok_seq || !seq_slot)) return kBadArgument;
   cudaStream_t st = (cudaStream_t)stream;
+  // a CTA per token while the tokens are few (a decode step: its latency is what counts), a
+  // warp per token for a prompt's rows
 #define CRETIF_LAT(TI, TT)                                                                      \
-  latent_in_kernel<TI, TT><<<T, 256, 0, st>>>(                                                  \
-      (const TI*)proj, ldp, q_rank, rank, rot, wq, wc, eps, cos_t, sin_t, pairing, tok_pos,      \
-      tok_seq, seq_slot, (TT*)cq_out, ldq, table, table_stride, (TT*)kc, bt, write_cache, fault)
+  do {                                                                                          \
+    if (T < 256)                                                                                \
+      latent_in_kernel<TI, TT><<<T, 256, 0, st>>>(                                              \
+          (const TI*)proj, ldp, q_rank, rank, rot, wq, wc, eps, cos_t, sin_t, pairing, tok_pos,  \
+          tok_seq, seq_slot, (TT*)cq_out, ldq, table, table_stride, (TT*)kc, bt, write_cache,    \
+          fault);                                                                               \
+    else                                                                                        \
+      latent_in_rows_kernel<TI, TT><<<(unsigned)((T + 7) / 8), 256, 0, st>>>(                    \
+          (const TI*)proj, ldp, q_rank, rank, rot, wq, wc, eps, cos_t, sin_t, pairing, tok_pos,  \
+          tok_seq, seq_slot, (TT*)cq_out, ldq, table, table_stride, (TT*)kc, bt, write_cache, T, \
+          fault);                                                                               \
+  } while (0)
   if (proj_dt == kF32 && dt == kF32) CRETIF_LAT(float, float);
   else if (proj_dt == kF32 && dt == kBF16) CRETIF_LAT(float, __nv_bfloat16);
   else if (proj_dt == kBF16 && dt == kBF16) CRETIF_LAT(__nv_bfloat16, __nv_bfloat16);
@@ -185,10 +281,18 @@ extern "C" int cretif_rope_heads(const void* q, int ldq, int q_dt, int nh, int d
   const long long items = (long long)T * nh;
   const unsigned blocks = (unsigned)((items + 7) / 8);
   cudaStream_t st = (cudaStream_t)stream;
+  const long long pairs = items * (rot / 2);
 #define CRETIF_RH(TI, TT)                                                                       \
-  rope_heads_kernel<TI, TT><<<blocks, 256, 0, st>>>((const TI*)q, ldq, nh, d, rot, cos_t, sin_t, \
-                                                    pairing, tok_pos, (TT*)out, ldo, ldh, off,  \
-                                                    items)
+  do {                                                                                          \
+    if (T < 256)                                                                                \
+      rope_heads_kernel<TI, TT><<<blocks, 256, 0, st>>>((const TI*)q, ldq, nh, d, rot, cos_t,   \
+                                                        sin_t, pairing, tok_pos, (TT*)out, ldo, \
+                                                        ldh, off, items);                       \
+    else                                                                                        \
+      rope_pairs_kernel<TI, TT><<<(unsigned)((pairs + 255) / 256), 256, 0, st>>>(               \
+          (const TI*)q, ldq, nh, d, rot, cos_t, sin_t, pairing, tok_pos, (TT*)out, ldo, ldh,    \
+          off, pairs);                                                                          \
+  } while (0)
   if (q_dt == kF32 && dt == kF32) CRETIF_RH(float, float);
   else if (q_dt == kF32 && dt == kBF16) CRETIF_RH(float, __nv_bfloat16);
   else if (q_dt == kBF16 && dt == kBF16) CRETIF_RH(__nv_bfloat16, __nv_bfloat16);

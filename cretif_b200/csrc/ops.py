@@ -1164,8 +1164,10 @@ def decode_plan(B: int, nkv: int, max_context: int, device, hd: int = 64):
 def attn_decode(q, out, kc, vc, table, tok_pos, tok_seq, seq_slot, nh: int, nkv: int, hd: int,
                 scale: float, window: int, block_tokens: int, n_splits: int, fault,
                 cluster: bool = False, sink=None, bias_near=None, bias_far=None,
-                head_groups: int = 1) -> None:
-    """``head_groups`` = G > 1 (tensor-core kernel only): more than eight query heads on a
+                head_groups: int = 1, bias_slope=None) -> None:
+    """``bias_slope`` (float32 [heads], times log2 e; tensor-core kernel only, not with the
+    table): the key n positions back has n times it taken off its scaled score.
+    ``head_groups`` = G > 1 (tensor-core kernel only): more than eight query heads on a
     key/value head in ONE launch; the rows of ``q``, ``out``, ``tok_pos`` and ``tok_seq`` are
     (sequence, group of ``nh`` heads) items, G of them a sequence, while ``sink`` and the bias
     keep a row per head of all G·nh.  ``sink`` (float32 [heads], optional; tensor-core kernel only): exp(sink_h) joins head h's
@@ -1184,6 +1186,12 @@ def attn_decode(q, out, kc, vc, table, tok_pos, tok_seq, seq_slot, nh: int, nkv:
         _need(sink, "sink", torch.float32, 1)
         if sink.numel() != nh * head_groups or hd > 128 or _decode_simt_only:
             raise KernelError("attn_decode: a sink needs one number per head and head_dim <= 128")
+    if bias_slope is not None:
+        _need(bias_slope, "bias_slope", torch.float32, 1)
+        if (bias_slope.numel() != nh * head_groups or not bias_slope.is_contiguous() or hd > 128
+                or _decode_simt_only or bias_near is not None):
+            raise KernelError("attn_decode: a slope has one number per head, needs head_dim <= "
+                              "128 and comes without a bias table")
     if head_groups > 1 and (hd > 128 or _decode_simt_only or q.shape[0] % head_groups):
         raise KernelError("attn_decode: groups of heads need head_dim <= 128 and whole "
                           "sequences of items")
@@ -1203,8 +1211,8 @@ def attn_decode(q, out, kc, vc, table, tok_pos, tok_seq, seq_slot, nh: int, nkv:
             _p(q), _rows(q, "q"), _p(out), _rows(out, "out"), _p(kc), _p(vc),
             ctypes.c_longlong(kc.shape[0]), _p(table), table.stride(0), _p(tok_pos), _p(tok_seq),
             _p(seq_slot), nh, nkv, hd, ctypes.c_float(scale), window, block_tokens, B, n_splits,
-            None, None, None, _p(sink), _p(bias_near), _p(bias_far), n_far, head_groups, _p(fault),
-            _stream()),
+            None, None, None, _p(sink), _p(bias_near), _p(bias_far), n_far, head_groups,
+            _p(bias_slope), _p(fault), _stream()),
             "attn_decode_mma")
         return
     part_o = torch.empty((B, nh, n_splits, hd), dtype=torch.float32, device=q.device)
@@ -1216,7 +1224,7 @@ def attn_decode(q, out, kc, vc, table, tok_pos, tok_seq, seq_slot, nh: int, nkv:
             ctypes.c_longlong(kc.shape[0]), _p(table), table.stride(0), _p(tok_pos), _p(tok_seq),
             _p(seq_slot), nh, nkv, hd, ctypes.c_float(scale), window, block_tokens, B, n_splits,
             _p(part_o), _p(part_ml), _p(counters), _p(sink), _p(bias_near), _p(bias_far), n_far,
-            head_groups, _p(fault), _stream()), "attn_decode_mma")
+            head_groups, _p(bias_slope), _p(fault), _stream()), "attn_decode_mma")
         return
     _check(lib().cretif_attn_decode(
         _p(q), _rows(q, "q"), _p(out), _rows(out, "out"), _p(kc), _p(vc), _p(table),
@@ -1442,11 +1450,12 @@ def attn_prefill_supported(hd: int, block_tokens: int) -> bool:
 
 def attn_prefill(qkv, out, kc, vc, table, cu_seqlens, seq_start, seq_slot, nh: int, nkv: int,
                  hd: int, scale: float, window: int, block_tokens: int, B: int, max_new: int,
-                 fault, sink=None, bias_near=None, bias_far=None) -> None:
+                 fault, sink=None, bias_near=None, bias_far=None, bias_slope=None) -> None:
     """Causal attention of whole prompts; ``qkv`` rows start with the query heads.  ``sink``
     (float32 [heads], optional): exp(sink_h) joins head h's softmax denominator.  ``bias_near``
     [heads, n_far] with ``bias_far`` [heads] (float32, times log2 e): what the key n positions
-    back adds to its scaled score, for n < n_far and for every n beyond."""
+    back adds to its scaled score, for n < n_far and for every n beyond.  ``bias_slope`` (float32
+    [heads], times log2 e; not with the table): n times it is taken off that score instead."""
     n_far = 0
     if bias_near is not None:
         _need(bias_near, "bias_near", torch.float32, 2); _need(bias_far, "bias_far", torch.float32, 1)
@@ -1455,6 +1464,11 @@ def attn_prefill(qkv, out, kc, vc, table, cu_seqlens, seq_start, seq_slot, nh: i
                 or not bias_far.is_contiguous()):
             raise KernelError("attn_prefill: the bias is [heads, distances] with one far value "
                               "per head")
+    if bias_slope is not None:
+        _need(bias_slope, "bias_slope", torch.float32, 1)
+        if bias_slope.numel() != nh or not bias_slope.is_contiguous() or bias_near is not None:
+            raise KernelError("attn_prefill: a slope has one number per head and comes without "
+                              "a bias table")
     if sink is not None:
         _need(sink, "sink", torch.float32, 1)
         if sink.numel() != nh:
@@ -1468,4 +1482,5 @@ def attn_prefill(qkv, out, kc, vc, table, cu_seqlens, seq_start, seq_slot, nh: i
         _p(qkv), _rows(qkv, "qkv"), qkv.shape[0], _p(out), _rows(out, "out"), _p(kc), _p(vc),
         ctypes.c_longlong(kc.shape[0]), _p(table), table.stride(0), _p(cu_seqlens), _p(seq_start),
         _p(seq_slot), nh, nkv, hd, ctypes.c_float(scale), window, block_tokens, B, max_new,
-        _p(sink), _p(bias_near), _p(bias_far), n_far, _p(fault), _stream()), "attn_prefill_tc")
+        _p(sink), _p(bias_near), _p(bias_far), n_far, _p(bias_slope), _p(fault), _stream()),
+        "attn_prefill_tc")

@@ -90,19 +90,8 @@ def distance_edges(rows: int, far: float):
 FAST_BIAS_MAX_DISTANCES = 4096
 
 
-def slope_table(slopes, distances: int):
-    """A slope by distance as the tensor-core kernels take a bias: (near [heads, distances],
-    far [heads]), times log2 e; ``far`` stands for every distance from ``distances`` on, which a
-    window or a chunk of at most that many keys never shows."""
-    log2e = 1.4426950408889634
-    n = torch.arange(distances, dtype=torch.float64, device=slopes.device)
-    near = (-(slopes.double()[:, None] * n[None, :]) * log2e).float().contiguous()
-    far = (-(slopes.double() * distances) * log2e).float().contiguous()
-    return near, far
-
-
 def run_attention(q, o, ctx, kv, nh, nkv, hd, scale, window, dtype, sink=None, vd=0, bias=None,
-                  bias_edges=None, bias_dense=None, slope=None):
+                  bias_edges=None, bias_dense=None, slope=None, slope_log2e=None):
     """Causal (windowed) attention of the step's queries ``q`` [T, nh·hd] over the cache view
     ``kv`` into ``o``, with the kernel that fits the step: the decode kernels when every
     sequence brings one token, the prompt kernel otherwise, the plain kernel for float32 and
@@ -111,14 +100,15 @@ def run_attention(q, o, ctx, kv, nh, nkv, hd, scale, window, dtype, sink=None, v
     ``bias_edges`` is the bias by distance as the plain kernel takes it, ``bias_dense`` =
     (near [heads, n_far], far [heads]), times log2 e, as the tensor-core kernels do.  ``window``
     below zero stands for chunks of ``-window`` positions.  ``slope`` [heads]: a multiple of the
-    distance taken off the scores; the fast kernels take it as ``bias_dense`` (made by
-    ``slope_table`` when the mask bounds the distance), the plain kernel as it is."""
+    distance taken off the scores; the plain kernel takes it as it is, the fast kernels work in
+    powers of two and take ``slope_log2e``, the same numbers times log2 e."""
     vd = vd or hd
-    biased = bias is not None or slope is not None
     fast = (not _force_plain and dtype == torch.bfloat16 and (sink is None or hd <= 128)
             and vd == hd and not (bias is not None and slope is not None)
-            and (not biased or (bias_dense is not None and hd <= 128)))
-    near, far = bias_dense if (biased and bias_dense is not None) else (None, None)
+            and (bias is None or (bias_dense is not None and hd <= 128))
+            and (slope is None or (slope_log2e is not None and hd <= 128)))
+    near, far = bias_dense if (bias is not None and bias_dense is not None) else (None, None)
+    tilt = slope_log2e if slope is not None else None
     if fast:
         if ctx.is_decode and ops.attn_decode_supported(hd, kv.block_tokens, min(nh // nkv, 8)) \
                 and (nh // nkv <= 8 or nkv == 1):
@@ -138,7 +128,7 @@ def run_attention(q, o, ctx, kv, nh, nkv, hd, scale, window, dtype, sink=None, v
                 ops.attn_decode(q.view(ctx.B * G, 8 * hd), o.view(ctx.B * G, 8 * hd), kv.k, kv.v,
                                 kv.table, pos_g, seq_g, ctx.seq_slot, 8, 1, hd, scale, window,
                                 kv.block_tokens, splits, ctx.fault, cluster, sink=sink,
-                                bias_near=near, bias_far=far, head_groups=G)
+                                bias_near=near, bias_far=far, head_groups=G, bias_slope=tilt)
                 return
             # ... else eight at a time
             step = nh if nh // nkv <= 8 else 8
@@ -150,12 +140,14 @@ def run_attention(q, o, ctx, kv, nh, nkv, hd, scale, window, dtype, sink=None, v
                                 window, kv.block_tokens, splits, ctx.fault, cluster,
                                 sink=None if sink is None else sink[h0:h0 + n],
                                 bias_near=None if near is None else near[h0:h0 + n],
-                                bias_far=None if far is None else far[h0:h0 + n])
+                                bias_far=None if far is None else far[h0:h0 + n],
+                                bias_slope=None if tilt is None else tilt[h0:h0 + n])
             return
         if not ctx.is_decode and ops.attn_prefill_supported(hd, kv.block_tokens):
             ops.attn_prefill(q, o, kv.k, kv.v, kv.table, ctx.cu_seqlens, ctx.seq_start,
                              ctx.seq_slot, nh, nkv, hd, scale, window, kv.block_tokens, ctx.B,
-                             ctx.max_new, ctx.fault, sink=sink, bias_near=near, bias_far=far)
+                             ctx.max_new, ctx.fault, sink=sink, bias_near=near, bias_far=far,
+                             bias_slope=tilt)
             return
     ops.attn_simt(q, o, kv.k, kv.v, kv.table, ctx.tok_pos, ctx.tok_seq, ctx.seq_slot,
                   nh, nkv, hd, scale, window, kv.block_tokens, sink=sink, vd=vd, bias=bias,
@@ -219,7 +211,7 @@ class Attention(Part):
         self.head_gate = params.get("head_gate")
         # the family that norms head by head without a convolution
         self.slope_spec = params.get("distance_slope")
-        self.slope = None
+        self.slope = self.slope_log2e = None
         self.headwise = self.conv is None and bool(
             self.bias_names or self.head_gate or self.head_norm or self.vd != self.hd
             or self.chunk or self.slope_spec or not self.own_kv)
@@ -338,13 +330,9 @@ class Attention(Part):
         if self.slope_spec is not None:
             x = float(self.slope_spec["exponent"])
             hs = torch.arange(1, self.nh + 1, dtype=torch.float64)
-            self.slope = self._vector32(2.0 ** (-x * hs / self.nh))
-            # a window or a chunk bounds the distance: the tensor-core kernels then take the
-            # slope as a dense table of that many distances
-            span = self.chunk or self.window
-            if (self.bias is None and 1 <= span <= FAST_BIAS_MAX_DISTANCES
-                    and self.dtype == torch.bfloat16):
-                self.bias_dense = slope_table(self.slope, span)
+            slopes = 2.0 ** (-x * hs / self.nh)
+            self.slope = self._vector32(slopes)
+            self.slope_log2e = self._vector32(slopes * 1.4426950408889634)   # for exp2 kernels
         if self.params.get("fixed_sink") is not None:
             self.sink = torch.full((self.nh,), float(self.params["fixed_sink"]),
                                    dtype=torch.float32, device=self.device)
@@ -550,7 +538,8 @@ class Attention(Part):
     def attend(self, q, o, ctx, kv):
         run_attention(q, o, ctx, kv, self.nh, self.nkv, self.hd, self.scale, self.mask,
                       self.dtype, self.sink, vd=self.vd, bias=self.bias,
-                      bias_edges=self.bias_edges, bias_dense=self.bias_dense, slope=self.slope)
+                      bias_edges=self.bias_edges, bias_dense=self.bias_dense, slope=self.slope,
+                      slope_log2e=self.slope_log2e)
 
     def weight_bytes(self):
         return (self.w_qkv.numel() + self.w_o.numel()) * self.w_qkv.element_size()

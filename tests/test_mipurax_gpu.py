@@ -159,11 +159,12 @@ def _gather(cache, table, positions, bt=64):
 def test_the_latents_their_norms_the_rotated_part_and_the_cache_write(dtype, H, d, rot, rank,
                                                                       q_rank, layout):
     """The kernels between a latent attention's input product and its scores, over a sequence
-    fed in pieces, against the plain functions."""
+    fed in pieces (the long piece takes the kernels' many-token forms), against the plain
+    functions."""
     from cretif_b200.csrc import ops
     from cretif_b200.parts.position import rotary_table
     g = torch.Generator().manual_seed(4)
-    S, base, eps = 90, 300.0, 1e-5
+    S, base, eps = 300, 300.0, 1e-5
     proj = torch.randn(S, q_rank + rank + rot + 5, generator=g) * 2
     wq, wc = torch.randn(q_rank, generator=g), torch.randn(rank, generator=g)
     P = proj.double()
@@ -176,7 +177,7 @@ def test_the_latents_their_norms_the_rotated_part_and_the_cache_write(dtype, H, 
     cq_out = torch.zeros(S, q_rank, dtype=dtype, device="cuda")
     fault = torch.zeros(1, dtype=torch.int32, device="cuda")
     at = 0
-    for n in (1, 2, 30, 1, 56):
+    for n in (1, 2, 30, 1, 266):
         pos = torch.arange(at, at + n, dtype=torch.int32, device="cuda")
         zeros = torch.zeros(n, dtype=torch.int32, device="cuda")
         ops.latent_in(proj[at:at + n].cuda(), q_rank, rank, rot, wq.cuda(), wc.cuda(), eps, cos,
@@ -197,6 +198,9 @@ def test_the_latents_their_norms_the_rotated_part_and_the_cache_write(dtype, H, 
     want = plain.rotate(q.double().view(S, H, d + rot)[..., d:], base, rot, layout)
     assert (q_lat[:, :, rank:].cpu().double() - want).abs().max() < tol
     assert bool((q_lat[:, :, :rank] == 0).all())
+    few = torch.zeros(40, H, rank + rot, dtype=dtype, device="cuda")
+    ops.rope_heads(q[200:240].cuda(), H, d, rot, cos, sin, pairing, pos[200:240], few, rank)
+    assert torch.equal(few, q_lat[200:240])
 
 
 @pytest.mark.parametrize("E,top,groups,keep", [(8, 2, 4, 2), (12, 2, 4, 3), (6, 3, 2, 2),
@@ -264,7 +268,7 @@ def test_attention_kernels_with_chunks_and_a_slope(H, G, d, chunk):
     """The attention kernels the engine picks in bfloat16 (prompt, portion, single tokens) and
     the plain kernel in float32, with a chunked mask and a slope by distance, against the plain
     softmax on the same inputs."""
-    from cretif_b200.parts.attention import run_attention, slope_table
+    from cretif_b200.parts.attention import run_attention
     from cretif_b200.parts.base import StepContext
     S = 333
     q, k, v = _attention_case(H, G, d, chunk, S, 7)
@@ -288,7 +292,7 @@ def test_attention_kernels_with_chunks_and_a_slope(H, G, d, chunk):
         kv = KV()
         kv.k, kv.v, kv.table, kv.block_tokens, kv.window = kc, vc, table, 64, 0
         slope = slopes.float().cuda()
-        dense = slope_table(slope, chunk) if dtype == torch.bfloat16 else None
+        tilt = (slopes * 1.4426950408889634).float().cuda()
 
         def ctx(T, first, decode):
             return StepContext(T=T, B=1, tok_ids=torch.zeros(T, **i32),
@@ -303,7 +307,7 @@ def test_attention_kernels_with_chunks_and_a_slope(H, G, d, chunk):
             out = torch.zeros(T, H * d, dtype=dtype, device=dev)
             run_attention(qd[first:first + T].reshape(T, H * d).cuda(), out,
                           ctx(T, first, decode), kv, H, G, d, scale, -chunk, dtype, None,
-                          slope=slope, bias_dense=dense)
+                          slope=slope, slope_log2e=tilt)
             err = (out.cpu().double() - want[first:first + T]).abs().max()
             tol = 1e-5 if dtype == torch.float32 else 2e-2
             assert err <= tol * want.abs().max(), (dtype, first, T, decode, float(err))
