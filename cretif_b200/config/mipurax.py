@@ -9,8 +9,9 @@ key                    meaning
 vocab, width           vocabulary and residual width
 norm.eps               eps of every RMS norm of the model
 layers[i].type         ``latent_attention`` | ``latent_attention_2`` | ``attention``
-layers[i].mixer        latent kinds: heads, dim (flat query/key size per head), rot_dim (rotated
-                       size), vdim, kv_rank, q_rank, scale, rot {base, dims};
+layers[i].mixer        latent kinds: heads, dim (flat query/key size per head), rot_dim (size of
+                       the rotated part), vdim, kv_rank, q_rank, scale, rot {base, dims} (dims:
+                       how many of the part's first channels turn; the design has all);
                        attention: heads, kv_heads, dim, vdim, scale, mask.size (the chunk),
                        kv_from (optional: the layer whose keys and values this layer reads
                        instead of projecting its own)
@@ -93,9 +94,10 @@ def _check_latent(i: int, m: Dict[str, Any]) -> None:
     rot = m.get("rot")
     _number(where + ".rot", rot, "base", positive=True)
     dims = _positive_int(where + ".rot", rot, "dims")
-    if dims != m["rot_dim"] or dims % 2:
-        raise ConfigError(f"{where}: rot.dims ({dims}) must be even and equal rot_dim "
-                          f"({m['rot_dim']}): the rotated part is rotated whole")
+    if dims > m["rot_dim"] or dims % 2:
+        raise ConfigError(f"{where}: rot.dims ({dims}) must be even and at most rot_dim "
+                          f"({m['rot_dim']}): the rotation turns the first channels of the "
+                          "rotated part")
 
 
 def _check_attention(i: int, m: Dict[str, Any], layers: List[Any]) -> None:
@@ -199,7 +201,7 @@ def _mixer_spec(kind: str, m: Dict[str, Any], eps: float) -> PartSpec:
         "latent_rank": m["kv_rank"], "q_rank": m["q_rank"], "rot_dim": m["rot_dim"],
         "scale": float(m["scale"]), "window": 0, "eps": eps, "gate": fixed["gate"],
         "position": {"kind": "rotary", "theta": float(m["rot"]["base"]),
-                     "pairing": fixed["pairing"]},
+                     "rotary_dim": int(m["rot"]["dims"]), "pairing": fixed["pairing"]},
         "names": names})
 
 

@@ -121,18 +121,18 @@ int cretif_general_delta_recurrence(const float* proj, int ldp, const float* pre
 // Attention over a cached latent (latent_ops.cu).  A projection row holds
 // [cq (q_rank) | c (rank) | kr (rot) | ...]: cq and c are brought to unit RMS and multiplied by wq
 // and wc, kr is rotated by the token's position; cq goes to cq_out, [c | kr] into the token's row
-// of the key cache (one key/value head of size rank + rot).  pairing 0: channel i with
-// i + rot/2, 1: channel 2i with 2i + 1.
+// of the key cache (one key/value head of size rank + rot).  Of the rot channels the first rdims
+// are rotated, the rest pass; pairing 0: channel i with i + rdims/2, 1: channel 2i with 2i + 1.
 int cretif_latent_in(const void* proj, int ldp, int proj_dt, int q_rank, int rank, int rot,
-                     const float* wq, const float* wc, float eps, const float* cos_t,
+                     int rdims, const float* wq, const float* wc, float eps, const float* cos_t,
                      const float* sin_t, int pairing, const int* tok_pos, const int* tok_seq,
                      const int* seq_slot, void* cq_out, int ldq, int dt, const int* table,
                      int table_stride, void* kc, int bt, int write_cache, int T,
                      unsigned int* fault, void* stream);
-// q [T, nh (d + rot)]: the last rot channels of every head, rotated, go to
-// out[t, h * ldh + off ...].
-int cretif_rope_heads(const void* q, int ldq, int q_dt, int nh, int d, int rot, const float* cos_t,
-                      const float* sin_t, int pairing, const int* tok_pos, void* out, int ldo,
+// q [T, nh (d + rot)]: the last rot channels of every head, the first rdims of them rotated, go
+// to out[t, h * ldh + off ...].
+int cretif_rope_heads(const void* q, int ldq, int q_dt, int nh, int d, int rot, int rdims,
+                      const float* cos_t, const float* sin_t, int pairing, const int* tok_pos, void* out, int ldo,
                       int ldh, int off, int dt, int T, void* stream);
 // x <- x / sqrt(mean(x^2) + eps) * w in place, float32 rows.
 int cretif_rmsnorm_rows(float* x, int ld, const float* w, int R, int H, float eps, void* stream);

@@ -11,8 +11,9 @@
 // the token's position, goes to columns off .. off + rot of the head's row of `out` (whose heads
 // are `ldh` apart): the tail of the query in latent space.
 //
-// Rotation: pair j of the rot channels is (j, j + rot/2) (pairing 0) or (2j, 2j + 1) (pairing 1);
-// (u, v) becomes (u cos - v sin, v cos + u sin), cos/sin from a 32-bit table [positions, rot/2].
+// Rotation: of the rot channels of a rotated part the first rdims are rotated, the rest pass;
+// pair j is (j, j + rdims/2) (pairing 0) or (2j, 2j + 1) (pairing 1); (u, v) becomes
+// (u cos - v sin, v cos + u sin), cos/sin from a 32-bit table [positions, rdims/2].
 //
 // rmsnorm_rows: x <- x / sqrt(mean(x^2) + eps) * w in place on float32 rows (the norm of an
 // embedding's output, which stays in the 32-bit residual stream).
@@ -23,9 +24,10 @@ namespace cretif {
 
 namespace {
 
-__device__ __forceinline__ float rotated(const float* v, int i, int rot, int pairing,
+__device__ __forceinline__ float rotated(const float* v, int i, int rdims, int pairing,
                                          const float* c, const float* s) {
-  const int half = rot >> 1;
+  if (i >= rdims) return v[i];
+  const int half = rdims >> 1;
   const bool first = pairing ? !(i & 1) : i < half;
   const int j = pairing ? i >> 1 : (first ? i : i - half);
   const int partner = pairing ? i ^ 1 : (first ? i + half : i - half);
@@ -36,7 +38,7 @@ constexpr int kLatMaxRot = 512;
 
 template <typename TI, typename T>
 __global__ void __launch_bounds__(256)
-latent_in_kernel(const TI* __restrict__ proj, int ldp, int q_rank, int rank, int rot,
+latent_in_kernel(const TI* __restrict__ proj, int ldp, int q_rank, int rank, int rot, int rdims,
                  const float* __restrict__ wq, const float* __restrict__ wc, float eps,
                  const float* __restrict__ cos_t, const float* __restrict__ sin_t, int pairing,
                  const int* __restrict__ tok_pos, const int* __restrict__ tok_seq,
@@ -85,10 +87,10 @@ latent_in_kernel(const TI* __restrict__ proj, int ldp, int q_rank, int rank, int
   T* dst = kc + ((size_t)blk * bt + (pos % bt)) * (rank + rot);
   for (int i = threadIdx.x; i < rank; i += blockDim.x)
     dst[i] = from_float<T>(to_float(crow[i]) * inv * wc[i]);
-  const float* c = cos_t + (size_t)pos * (rot >> 1);
-  const float* s = sin_t + (size_t)pos * (rot >> 1);
+  const float* c = cos_t + (size_t)pos * (rdims >> 1);
+  const float* s = sin_t + (size_t)pos * (rdims >> 1);
   for (int i = threadIdx.x; i < rot; i += blockDim.x)
-    dst[rank + i] = from_float<T>(rotated(kr, i, rot, pairing, c, s));
+    dst[rank + i] = from_float<T>(rotated(kr, i, rdims, pairing, c, s));
 }
 
 // The same for many tokens: a warp per token, no barrier; the second pass over the row finds it
@@ -96,7 +98,8 @@ latent_in_kernel(const TI* __restrict__ proj, int ldp, int q_rank, int rank, int
 template <typename TI, typename T>
 __global__ void __launch_bounds__(256)
 latent_in_rows_kernel(const TI* __restrict__ proj, int ldp, int q_rank, int rank, int rot,
-                      const float* __restrict__ wq, const float* __restrict__ wc, float eps,
+                      int rdims, const float* __restrict__ wq, const float* __restrict__ wc,
+                      float eps,
                       const float* __restrict__ cos_t, const float* __restrict__ sin_t,
                       int pairing, const int* __restrict__ tok_pos,
                       const int* __restrict__ tok_seq, const int* __restrict__ seq_slot,
@@ -139,11 +142,15 @@ latent_in_rows_kernel(const TI* __restrict__ proj, int ldp, int q_rank, int rank
   T* dst = kc + ((size_t)blk * bt + (pos % bt)) * (rank + rot);
 #pragma unroll 4
   for (int i = lane; i < rank; i += 32) dst[i] = from_float<T>(to_float(crow[i]) * inv * wc[i]);
-  const int half = rot >> 1;
+  const int half = rdims >> 1;
   const float* c = cos_t + (size_t)pos * half;
   const float* s = sin_t + (size_t)pos * half;
   const TI* kr = crow + rank;
   for (int i = lane; i < rot; i += 32) {
+    if (i >= rdims) {                      // beyond the rotated channels: as it is
+      dst[rank + i] = from_float<T>(to_float(kr[i]));
+      continue;
+    }
     const bool first = pairing ? !(i & 1) : i < half;
     const int j = pairing ? i >> 1 : (first ? i : i - half);
     const int partner = pairing ? i ^ 1 : (first ? i + half : i - half);
@@ -155,23 +162,29 @@ latent_in_rows_kernel(const TI* __restrict__ proj, int ldp, int q_rank, int rank
 // many tokens: a thread per (token, head, pair of channels)
 template <typename TI, typename T>
 __global__ void __launch_bounds__(256)
-rope_pairs_kernel(const TI* __restrict__ q, int ldq, int nh, int d, int rot,
+rope_pairs_kernel(const TI* __restrict__ q, int ldq, int nh, int d, int rot, int rdims,
                   const float* __restrict__ cos_t, const float* __restrict__ sin_t, int pairing,
                   const int* __restrict__ tok_pos, T* __restrict__ out, int ldo, int ldh, int off,
                   long long total) {
   const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= total) return;
-  const int half = rot >> 1;
-  const int j = (int)(idx % half);
-  const long long th = idx / half;
+  const int slots = rot >> 1, half = rdims >> 1;
+  const int j = (int)(idx % slots);
+  const long long th = idx / slots;
   const int h = (int)(th % nh);
   const long long t = th / nh;
-  const int a = pairing ? 2 * j : j, b = pairing ? 2 * j + 1 : j + half;
   const TI* src = q + (size_t)t * ldq + (size_t)h * (d + rot) + d;
+  T* dst = out + (size_t)t * ldo + (size_t)h * ldh + off;
+  if (j >= half) {                         // two of the channels that pass as they are
+    const int a = rdims + 2 * (j - half);
+    dst[a] = from_float<T>(to_float(src[a]));
+    dst[a + 1] = from_float<T>(to_float(src[a + 1]));
+    return;
+  }
+  const int a = pairing ? 2 * j : j, b = pairing ? 2 * j + 1 : j + half;
   const float u = to_float(src[a]), v = to_float(src[b]);
   const int pos = tok_pos[t];
   const float c = cos_t[(size_t)pos * half + j], s = sin_t[(size_t)pos * half + j];
-  T* dst = out + (size_t)t * ldo + (size_t)h * ldh + off;
   dst[a] = from_float<T>(u * c - v * s);
   dst[b] = from_float<T>(v * c + u * s);
 }
@@ -179,7 +192,7 @@ rope_pairs_kernel(const TI* __restrict__ q, int ldq, int nh, int d, int rot,
 // a warp per (token, head)
 template <typename TI, typename T>
 __global__ void __launch_bounds__(256)
-rope_heads_kernel(const TI* __restrict__ q, int ldq, int nh, int d, int rot,
+rope_heads_kernel(const TI* __restrict__ q, int ldq, int nh, int d, int rot, int rdims,
                   const float* __restrict__ cos_t, const float* __restrict__ sin_t, int pairing,
                   const int* __restrict__ tok_pos, T* __restrict__ out, int ldo, int ldh, int off,
                   long long items) {
@@ -193,10 +206,11 @@ rope_heads_kernel(const TI* __restrict__ q, int ldq, int nh, int d, int rot,
   for (int i = lane; i < rot; i += 32) mine[i] = to_float(src[i]);
   __syncwarp();
   const int pos = tok_pos[t];
-  const float* c = cos_t + (size_t)pos * (rot >> 1);
-  const float* s = sin_t + (size_t)pos * (rot >> 1);
+  const float* c = cos_t + (size_t)pos * (rdims >> 1);
+  const float* s = sin_t + (size_t)pos * (rdims >> 1);
   T* dst = out + (size_t)t * ldo + (size_t)h * ldh + off;
-  for (int i = lane; i < rot; i += 32) dst[i] = from_float<T>(rotated(mine, i, rot, pairing, c, s));
+  for (int i = lane; i < rot; i += 32)
+    dst[i] = from_float<T>(rotated(mine, i, rdims, pairing, c, s));
 }
 
 // a CTA per row, for a few rows: a lone warp would wait for its loads one after the other
@@ -234,16 +248,17 @@ rmsnorm_rows_kernel(float* __restrict__ x, int ld, const float* __restrict__ w, 
 using namespace cretif;
 
 extern "C" int cretif_latent_in(const void* proj, int ldp, int proj_dt, int q_rank, int rank,
-                                int rot, const float* wq, const float* wc, float eps,
+                                int rot, int rdims, const float* wq, const float* wc, float eps,
                                 const float* cos_t, const float* sin_t, int pairing,
                                 const int* tok_pos, const int* tok_seq, const int* seq_slot,
                                 void* cq_out, int ldq, int dt, const int* table, int table_stride,
                                 void* kc, int bt, int write_cache, int T, unsigned int* fault,
                                 void* stream) {
   if (T <= 0) return kOk;
-  if (q_rank < 0 || rank <= 0 || rot < 0 || rot > kLatMaxRot || (rot & 1) ||
-      ldp < q_rank + rank + rot || (q_rank > 0 && (!wq || !cq_out || ldq < q_rank)) || !wc ||
-      (rot > 0 && (!cos_t || !sin_t)))
+  if (q_rank < 0 || rank <= 0 || rot < 0 || rot > kLatMaxRot || (rot & 1) || rdims < 0 ||
+      rdims > rot || (rdims & 1) || ldp < q_rank + rank + rot ||
+      (q_rank > 0 && (!wq || !cq_out || ldq < q_rank)) || !wc ||
+      (rdims > 0 && (!cos_t || !sin_t)))
     return kBadArgument;
   if (write_cache && (bt <= 0 || !kc || !table || !tok_seq || !seq_slot)) return kBadArgument;
   cudaStream_t st = (cudaStream_t)stream;
@@ -253,14 +268,14 @@ extern "C" int cretif_latent_in(const void* proj, int ldp, int proj_dt, int q_ra
   do {                                                                                          \
     if (T < 256)                                                                                \
       latent_in_kernel<TI, TT><<<T, 256, 0, st>>>(                                              \
-          (const TI*)proj, ldp, q_rank, rank, rot, wq, wc, eps, cos_t, sin_t, pairing, tok_pos,  \
-          tok_seq, seq_slot, (TT*)cq_out, ldq, table, table_stride, (TT*)kc, bt, write_cache,    \
-          fault);                                                                               \
+          (const TI*)proj, ldp, q_rank, rank, rot, rdims, wq, wc, eps, cos_t, sin_t, pairing,    \
+          tok_pos, tok_seq, seq_slot, (TT*)cq_out, ldq, table, table_stride, (TT*)kc, bt,        \
+          write_cache, fault);                                                                    \
     else                                                                                        \
       latent_in_rows_kernel<TI, TT><<<(unsigned)((T + 7) / 8), 256, 0, st>>>(                    \
-          (const TI*)proj, ldp, q_rank, rank, rot, wq, wc, eps, cos_t, sin_t, pairing, tok_pos,  \
-          tok_seq, seq_slot, (TT*)cq_out, ldq, table, table_stride, (TT*)kc, bt, write_cache, T, \
-          fault);                                                                               \
+          (const TI*)proj, ldp, q_rank, rank, rot, rdims, wq, wc, eps, cos_t, sin_t, pairing,    \
+          tok_pos, tok_seq, seq_slot, (TT*)cq_out, ldq, table, table_stride, (TT*)kc, bt,        \
+          write_cache, T, fault);                                                                 \
   } while (0)
   if (proj_dt == kF32 && dt == kF32) CRETIF_LAT(float, float);
   else if (proj_dt == kF32 && dt == kBF16) CRETIF_LAT(float, __nv_bfloat16);
@@ -271,12 +286,13 @@ extern "C" int cretif_latent_in(const void* proj, int ldp, int proj_dt, int q_ra
 }
 
 extern "C" int cretif_rope_heads(const void* q, int ldq, int q_dt, int nh, int d, int rot,
-                                 const float* cos_t, const float* sin_t, int pairing,
+                                 int rdims, const float* cos_t, const float* sin_t, int pairing,
                                  const int* tok_pos, void* out, int ldo, int ldh, int off, int dt,
                                  int T, void* stream) {
   if (T <= 0 || rot == 0) return kOk;
-  if (nh <= 0 || d < 0 || rot < 0 || rot > kLatMaxRot || (rot & 1) || ldq < nh * (d + rot) ||
-      off < 0 || ldh < off + rot || ldo < (nh - 1) * ldh + off + rot || !cos_t || !sin_t)
+  if (nh <= 0 || d < 0 || rot < 0 || rot > kLatMaxRot || (rot & 1) || rdims < 0 || rdims > rot ||
+      (rdims & 1) || ldq < nh * (d + rot) || off < 0 || ldh < off + rot ||
+      ldo < (nh - 1) * ldh + off + rot || (rdims > 0 && (!cos_t || !sin_t)))
     return kBadArgument;
   const long long items = (long long)T * nh;
   const unsigned blocks = (unsigned)((items + 7) / 8);
@@ -285,13 +301,13 @@ extern "C" int cretif_rope_heads(const void* q, int ldq, int q_dt, int nh, int d
 #define CRETIF_RH(TI, TT)                                                                       \
   do {                                                                                          \
     if (T < 256)                                                                                \
-      rope_heads_kernel<TI, TT><<<blocks, 256, 0, st>>>((const TI*)q, ldq, nh, d, rot, cos_t,   \
-                                                        sin_t, pairing, tok_pos, (TT*)out, ldo, \
-                                                        ldh, off, items);                       \
+      rope_heads_kernel<TI, TT><<<blocks, 256, 0, st>>>((const TI*)q, ldq, nh, d, rot, rdims,   \
+                                                        cos_t, sin_t, pairing, tok_pos,         \
+                                                        (TT*)out, ldo, ldh, off, items);        \
     else                                                                                        \
       rope_pairs_kernel<TI, TT><<<(unsigned)((pairs + 255) / 256), 256, 0, st>>>(               \
-          (const TI*)q, ldq, nh, d, rot, cos_t, sin_t, pairing, tok_pos, (TT*)out, ldo, ldh,    \
-          off, pairs);                                                                          \
+          (const TI*)q, ldq, nh, d, rot, rdims, cos_t, sin_t, pairing, tok_pos, (TT*)out, ldo,  \
+          ldh, off, pairs);                                                                        \
   } while (0)
   if (q_dt == kF32 && dt == kF32) CRETIF_RH(float, float);
   else if (q_dt == kF32 && dt == kBF16) CRETIF_RH(float, __nv_bfloat16);

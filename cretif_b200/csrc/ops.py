@@ -409,9 +409,10 @@ def headnorm_rope_kv_append(proj, bias, wq, wk, eps: float, cos, sin, pairing: i
 
 def latent_in(proj, q_rank: int, rank: int, rot: int, wq, wc, eps: float, cos, sin, pairing: int,
               tok_pos, tok_seq, seq_slot, cq_out, table=None, kc=None, block_tokens: int = 64,
-              write_cache: bool = True, fault=None) -> None:
+              write_cache: bool = True, fault=None, rot_dims: Optional[int] = None) -> None:
     """``proj`` rows [cq (q_rank) | c (rank) | kr (rot) | ...] (float32, or the cache's type):
-    cq and c to unit RMS times ``wq`` / ``wc`` (float32), kr rotated by the position; cq to
+    cq and c to unit RMS times ``wq`` / ``wc`` (float32), kr rotated by the position (its first
+    ``rot_dims`` channels, all of them by default; the rest pass); cq to
     ``cq_out`` [T, q_rank] (``q_rank`` 0: no query latent), [c | kr] into the token's row of the
     key cache ``kc`` [blocks, 1, block_tokens, rank + rot]."""
     _need(proj, "proj", dim=2); _need(wc, "wc", torch.float32, 1)
@@ -427,10 +428,13 @@ def latent_in(proj, q_rank: int, rank: int, rot: int, wq, wc, eps: float, cos, s
         if wq.numel() != q_rank or cq_out.shape[0] != T or cq_out.shape[1] < q_rank \
                 or not wq.is_contiguous():
             raise KernelError("latent_in: the query latent's weight and output have q_rank columns")
-    if rot:
+    rdims = rot if rot_dims is None else int(rot_dims)
+    if not 0 <= rdims <= rot or rdims % 2:
+        raise KernelError("latent_in: rot_dims is even and at most rot")
+    if rdims:
         _need(cos, "cos", torch.float32, 2); _need(sin, "sin", torch.float32, 2)
-        if cos.shape[1] != rot // 2 or not cos.is_contiguous() or not sin.is_contiguous():
-            raise KernelError("latent_in: cos/sin must be contiguous [positions, rot/2]")
+        if cos.shape[1] != rdims // 2 or not cos.is_contiguous() or not sin.is_contiguous():
+            raise KernelError("latent_in: cos/sin must be contiguous [positions, rot_dims/2]")
     else:
         cos = sin = None
     if write_cache:
@@ -441,16 +445,17 @@ def latent_in(proj, q_rank: int, rank: int, rot: int, wq, wc, eps: float, cos, s
     if fault is None:
         fault = fault_word(proj.device)
     _check(lib().cretif_latent_in(
-        _p(proj), _rows(proj, "proj"), _dt(proj), q_rank, rank, rot, _p(wq), _p(wc),
+        _p(proj), _rows(proj, "proj"), _dt(proj), q_rank, rank, rot, rdims, _p(wq), _p(wc),
         ctypes.c_float(eps), _p(cos), _p(sin), pairing, _p(tok_pos), _p(tok_seq), _p(seq_slot),
         _p(cq_out), _rows(cq_out, "cq_out") if q_rank else 0, _DT[dt], _p(table),
         table.stride(0) if table is not None else 0, _p(kc), block_tokens, int(write_cache), T,
         _p(fault), _stream()), "latent_in")
 
 
-def rope_heads(q, nh: int, d: int, rot: int, cos, sin, pairing: int, tok_pos, out, off: int) -> None:
+def rope_heads(q, nh: int, d: int, rot: int, cos, sin, pairing: int, tok_pos, out, off: int,
+               rot_dims: Optional[int] = None) -> None:
     """``q`` [T, nh·(d + rot)]: the last ``rot`` channels of every head, rotated by the token's
-    position, go to ``out[t, h, off : off + rot]`` (``out`` [T, nh, width >= off + rot], of the
+    position (the first ``rot_dims`` of them, all by default; the rest pass), go to ``out[t, h, off : off + rot]`` (``out`` [T, nh, width >= off + rot], of the
     compute type; ``q`` float32 or of that type)."""
     _need(q, "q", dim=2); _need(out, "out", dim=3)
     T = q.shape[0]
@@ -460,11 +465,17 @@ def rope_heads(q, nh: int, d: int, rot: int, cos, sin, pairing: int, tok_pos, ou
         raise KernelError("rope_heads: sizes or element types do not fit")
     if rot == 0:
         return
-    _need(cos, "cos", torch.float32, 2); _need(sin, "sin", torch.float32, 2)
-    if cos.shape[1] != rot // 2 or not cos.is_contiguous() or not sin.is_contiguous():
-        raise KernelError("rope_heads: cos/sin must be contiguous [positions, rot/2]")
+    rdims = rot if rot_dims is None else int(rot_dims)
+    if not 0 <= rdims <= rot or rdims % 2:
+        raise KernelError("rope_heads: rot_dims is even and at most rot")
+    if rdims:
+        _need(cos, "cos", torch.float32, 2); _need(sin, "sin", torch.float32, 2)
+        if cos.shape[1] != rdims // 2 or not cos.is_contiguous() or not sin.is_contiguous():
+            raise KernelError("rope_heads: cos/sin must be contiguous [positions, rot_dims/2]")
+    else:
+        cos = sin = None
     _check(lib().cretif_rope_heads(
-        _p(q), _rows(q, "q"), _dt(q), nh, d, rot, _p(cos), _p(sin), pairing, _p(tok_pos), _p(out),
+        _p(q), _rows(q, "q"), _dt(q), nh, d, rot, rdims, _p(cos), _p(sin), pairing, _p(tok_pos), _p(out),
         out.stride(0), out.stride(1), off, _dt(out), T, _stream()), "rope_heads")
 
 

@@ -43,7 +43,9 @@ class LatentAttention(Part):
     ``latent_rank``, ``scale``, ``window`` (0 = all keys), ``eps`` (of the latent's norm),
     ``names`` (q, down, down_norm, up_k, up_v, o and, optionally, sink).  Optional: ``q_rank``
     (the queries' latent; names q_down, q_norm, q_up instead of q), ``rot_dim`` with ``position``
-    (a rotary position part's constants), ``gate`` ("channel" | "head", name ``gate``)."""
+    (a rotary position part's constants; its ``rotary_dim``, by default all of ``rot_dim``, says
+    how many of the rotated part's first channels turn), ``gate`` ("channel" | "head", name
+    ``gate``)."""
 
     graph_safe = True
 
@@ -78,7 +80,10 @@ class LatentAttention(Part):
             if pos.pop("kind", "rotary") != "rotary" or self.rot % 2:
                 raise ValueError("latent_attention: the rotated part takes a rotary position "
                                  "encoding of an even size")
-            pos["rotary_dim"] = self.rot
+            pos["rotary_dim"] = int(pos.get("rotary_dim") or self.rot)
+            if not 0 < pos["rotary_dim"] <= self.rot or pos["rotary_dim"] % 2:
+                raise ValueError("latent_attention: the rotation takes an even number of the "
+                                 "rotated part's channels")
             self.position = build_part("position", PartSpec("rotary", pos), hidden_size, dtype,
                                        device)
         self.sink = None
@@ -140,9 +145,9 @@ class LatentAttention(Part):
         H, d, e, r, rot, T, D = self.nh, self.hd, self.vd, self.rank, self.rot, ctx.T, self.key_dim
         kv = cache.kv
         cos = sin = None
-        pairing = 0
+        pairing = rdims = 0
         if self.position is not None:
-            cos, sin, pairing, _ = self.position.rotary_table()
+            cos, sin, pairing, rdims = self.position.rotary_table()
         if proj is None:
             proj = linear(x, self.w_in, out_dtype=torch.float32)    # [cq | c | kr | gates | 0]
         dev = proj.device
@@ -150,11 +155,11 @@ class LatentAttention(Part):
         ops.latent_in(proj, self.q_rank, r, rot, self.q_norm, self.down_norm, self.eps, cos, sin,
                       pairing, ctx.tok_pos, ctx.tok_seq, ctx.seq_slot, cq, table=kv.table,
                       kc=kv.k, block_tokens=kv.block_tokens, write_cache=cache.writes,
-                      fault=ctx.fault)
+                      fault=ctx.fault, rot_dims=rdims)
         q = linear(cq, self.w_q_up)                                   # [T, H (d + rot)]
         q_lat = torch.empty((T, H, D), dtype=self.dtype, device=dev)
         ops.gemm_batched(q.view(T, H, d + rot)[:, :, :d], self.w_q_latent, q_lat[:, :, :r])
-        ops.rope_heads(q, H, d, rot, cos, sin, pairing, ctx.tok_pos, q_lat, r)
+        ops.rope_heads(q, H, d, rot, cos, sin, pairing, ctx.tok_pos, q_lat, r, rot_dims=rdims)
         o_lat = torch.empty((T, H * D), dtype=self.dtype, device=dev)
         run_attention(q_lat.view(T, H * D), o_lat, ctx, kv, H, 1, D, self.scale, self.window,
                       self.dtype, self.sink)

@@ -2,9 +2,9 @@
 import numpy as np
 
 
-def _lat(heads, dim, rot, vdim, kv_rank, q_rank, scale, base=10000.0):
+def _lat(heads, dim, rot, vdim, kv_rank, q_rank, scale, base=10000.0, dims=None):
     return {"heads": heads, "dim": dim, "rot_dim": rot, "vdim": vdim, "kv_rank": kv_rank,
-            "q_rank": q_rank, "scale": scale, "rot": {"base": base, "dims": rot}}
+            "q_rank": q_rank, "scale": scale, "rot": {"base": base, "dims": dims or rot}}
 
 
 def _att(heads, kv, dim, vdim, chunk, scale, kv_from=None):
@@ -53,22 +53,23 @@ M_B = _model(130, 96, 1e-6, [
     {"type": "latent_attention_2", "mixer": _lat(2, 32, 16, 24, 112, 64, 0.15), "mlp": None},
 ])
 # everything that can be one is one: one head, a chunk that shows a query nothing but itself, a
-# chunk of two, one expert, groups of one expert each, a rotated part of one pair
+# chunk of two, one expert, groups of one expert each, a rotated part of one pair, a rotated part
+# of which only the first pair turns
 M_C = _model(70, 48, 1e-5, [
     {"type": "attention", "mixer": _att(1, 1, 8, 8, 1, 1.0), "mlp": _moe(1, 1, 16)},
     {"type": "latent_attention_2", "mixer": _lat(1, 8, 2, 8, 8, 8, 0.5), "mlp": _ff(48)},
     {"type": "attention", "mixer": _att(1, 1, 16, 8, 2, 0.5),
      "mlp": _moe(4, 2, 24, groups=(4, 3), shared=8)},
-    {"type": "latent_attention", "mixer": _lat(1, 4, 4, 4, 12, 16, 0.4), "mlp": None},
+    {"type": "latent_attention", "mixer": _lat(1, 4, 4, 4, 12, 16, 0.4, dims=2), "mlp": None},
 ])
-# sizes that are multiples of nothing in particular: head sizes 12 and 20, a width of 40, an odd
-# vocabulary; a chunk longer than any test sequence; every group kept; a reader right after its
-# writer and a second reader of the same layer
-M_D = _model(77, 40, 1e-5, [
+# sizes that are multiples of nothing in particular: head sizes 12 and 20, a width of 36, an odd
+# vocabulary, ranks of 20 and 27; a chunk longer than any test sequence; every group kept; a
+# reader right after its writer and a second reader of the same layer
+M_D = _model(77, 36, 1e-5, [
     {"type": "attention", "mixer": _att(3, 1, 12, 20, 500, 0.29),
      "mlp": _moe(6, 3, 20, groups=(2, 2))},
     {"type": "attention", "mixer": _att(3, 1, 12, 20, 33, 0.3, kv_from=0), "mlp": None},
-    {"type": "latent_attention", "mixer": _lat(3, 12, 6, 10, 20, 28, 0.3, 77.0), "mlp": _ff(56)},
+    {"type": "latent_attention", "mixer": _lat(3, 12, 6, 10, 20, 27, 0.3, 77.0), "mlp": _ff(56)},
     {"type": "attention", "mixer": _att(3, 1, 12, 20, 64, 0.2, kv_from=0), "mlp": _ff(24)},
 ])
 

@@ -34,7 +34,8 @@ def test_parts_and_their_constants():
     assert lat.part.kind == "latent_attention" and p["gate"] == "channel"
     assert (p["q_rank"], p["latent_rank"], p["rot_dim"], p["head_dim"], p["value_dim"]) == \
         (40, 24, 8, 16, 24)
-    assert p["position"] == {"kind": "rotary", "theta": 10000.0, "pairing": "interleaved"}
+    assert p["position"] == {"kind": "rotary", "theta": 10000.0, "rotary_dim": 8,
+                             "pairing": "interleaved"}
     assert "sink" not in p["names"] and p["window"] == 0
     p2 = lat2.part.params
     assert p2["gate"] == "head" and p2["names"]["sink"] == "mix.sink"
@@ -88,7 +89,8 @@ def test_manifest_names_and_shapes():
 @pytest.mark.parametrize("edit, text", [
     (lambda c: c["layers"][0].update(type="retention"), "type"),
     (lambda c: c["layers"][0]["mixer"].pop("q_rank"), "q_rank"),
-    (lambda c: c["layers"][0]["mixer"]["rot"].update(dims=6), "rot.dims"),
+    (lambda c: c["layers"][0]["mixer"]["rot"].update(dims=10), "rot.dims"),
+    (lambda c: c["layers"][0]["mixer"]["rot"].update(dims=3), "rot.dims"),
     (lambda c: c["layers"][1]["mixer"].pop("mask"), "size"),
     (lambda c: c["layers"][1]["mixer"].update(kv_heads=3), "multiple"),
     (lambda c: c["layers"][3]["mixer"].update(kv_from=2), "kv_from"),

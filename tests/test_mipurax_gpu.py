@@ -153,11 +153,13 @@ def _gather(cache, table, positions, bt=64):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("H,d,rot,rank,q_rank,layout", [
-    (2, 16, 8, 24, 40, "interleaved"), (4, 8, 16, 48, 24, "half"), (1, 4, 2, 8, 8, "half"),
-    (3, 12, 6, 20, 28, "interleaved"), (2, 32, 64, 64, 96, "half"), (1, 8, 130, 300, 5, "half")])
+@pytest.mark.parametrize("H,d,rot,rank,q_rank,layout,dims", [
+    (2, 16, 8, 24, 40, "interleaved", 8), (4, 8, 16, 48, 24, "half", 16),
+    (1, 4, 2, 8, 8, "half", 2), (3, 12, 6, 20, 28, "interleaved", 6),
+    (2, 32, 64, 64, 96, "half", 64), (1, 8, 130, 300, 5, "half", 130),
+    (2, 8, 16, 24, 16, "half", 6), (3, 4, 12, 16, 8, "interleaved", 4)])
 def test_the_latents_their_norms_the_rotated_part_and_the_cache_write(dtype, H, d, rot, rank,
-                                                                      q_rank, layout):
+                                                                      q_rank, layout, dims):
     """The kernels between a latent attention's input product and its scores, over a sequence
     fed in pieces (the long piece takes the kernels' many-token forms), against the plain
     functions."""
@@ -170,8 +172,8 @@ def test_the_latents_their_norms_the_rotated_part_and_the_cache_write(dtype, H, 
     P = proj.double()
     cq = plain.unit(P[:, :q_rank], eps) * wq.double()
     c = plain.unit(P[:, q_rank:q_rank + rank], eps) * wc.double()
-    kr = plain.rotate(P[:, None, q_rank + rank:q_rank + rank + rot], base, rot, layout)[:, 0]
-    cos, sin = rotary_table(base, rot, S, torch.device("cuda"))
+    kr = plain.rotate(P[:, None, q_rank + rank:q_rank + rank + rot], base, dims, layout)[:, 0]
+    cos, sin = rotary_table(base, dims, S, torch.device("cuda"))
     pairing = 1 if layout == "interleaved" else 0
     kc, table = _cache_for(S, 1, rank + rot, dtype)
     cq_out = torch.zeros(S, q_rank, dtype=dtype, device="cuda")
@@ -182,7 +184,7 @@ def test_the_latents_their_norms_the_rotated_part_and_the_cache_write(dtype, H, 
         zeros = torch.zeros(n, dtype=torch.int32, device="cuda")
         ops.latent_in(proj[at:at + n].cuda(), q_rank, rank, rot, wq.cuda(), wc.cuda(), eps, cos,
                       sin, pairing, pos, zeros, zeros[:1], cq_out[at:at + n], table=table, kc=kc,
-                      fault=fault)
+                      fault=fault, rot_dims=dims)
         at += n
     assert at == S and int(fault.item()) == 0
     tol = 1e-4 if dtype == torch.float32 else 6e-2
@@ -194,12 +196,13 @@ def test_the_latents_their_norms_the_rotated_part_and_the_cache_write(dtype, H, 
     q = (torch.randn(S, H * (d + rot), generator=g) * 2).to(dtype)
     q_lat = torch.zeros(S, H, rank + rot, dtype=dtype, device="cuda")
     pos = torch.arange(S, dtype=torch.int32, device="cuda")
-    ops.rope_heads(q.cuda(), H, d, rot, cos, sin, pairing, pos, q_lat, rank)
-    want = plain.rotate(q.double().view(S, H, d + rot)[..., d:], base, rot, layout)
+    ops.rope_heads(q.cuda(), H, d, rot, cos, sin, pairing, pos, q_lat, rank, rot_dims=dims)
+    want = plain.rotate(q.double().view(S, H, d + rot)[..., d:], base, dims, layout)
     assert (q_lat[:, :, rank:].cpu().double() - want).abs().max() < tol
     assert bool((q_lat[:, :, :rank] == 0).all())
     few = torch.zeros(40, H, rank + rot, dtype=dtype, device="cuda")
-    ops.rope_heads(q[200:240].cuda(), H, d, rot, cos, sin, pairing, pos[200:240], few, rank)
+    ops.rope_heads(q[200:240].cuda(), H, d, rot, cos, sin, pairing, pos[200:240], few, rank,
+                   rot_dims=dims)
     assert torch.equal(few, q_lat[200:240])
 
 
