@@ -266,7 +266,8 @@ def _plain_chunked(q, k, v, chunk, scale, slopes):
 
 
 @pytest.mark.parametrize("H,G,d,chunk", [(4, 2, 64, 100), (2, 1, 128, 64), (8, 2, 32, 65),
-                                         (3, 3, 16, 129), (2, 2, 64, 1)])
+                                         (3, 3, 16, 129), (2, 2, 64, 1), (16, 1, 64, 100),
+                                         (24, 2, 32, 70), (12, 1, 48, 33)])
 def test_attention_kernels_with_chunks_and_a_slope(H, G, d, chunk):
     """The attention kernels the engine picks in bfloat16 (prompt, portion, single tokens) and
     the plain kernel in float32, with a chunked mask and a slope by distance, against the plain
